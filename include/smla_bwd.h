@@ -1,0 +1,99 @@
+/* C ABI of the B200 sparse MLA attention backward.
+ *
+ * Plain pointers and sizes only; every pointer is a device pointer unless stated.  The
+ * library never allocates device memory: the caller passes a workspace whose size it asks
+ * for first.  All entry points enqueue on the given CUDA stream and return without a host
+ * synchronisation except smla_bwd_status().
+ *
+ * Replaces, in the reference project MrChen314/test_operator:
+ *   - the host launchers `launch_preprocess_delta` and `launch_test_mla_bwd`
+ *     (mla_bwd/mla_bwd.cu:802-819, 822-969; prototype mla_bwd/mla_bwd.cuh:284-298), and
+ *   - the operator body `mla_bwd_forward` (mla_bwd/mla_bwd.cu:972-1058) apart from tensor
+ *     allocation, which stays with the caller.
+ */
+#ifndef SMLA_BWD_H_
+#define SMLA_BWD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMLA_D_QK 576          /* 512 latent + 64 rope (mla_bwd/mla_bwd.cuh:44-47) */
+#define SMLA_D_V 512
+#define SMLA_NO_CAUSAL INT32_MIN /* q_start_index_s value that switches the causal bound off */
+
+/* status codes */
+#define SMLA_OK 0
+#define SMLA_ERR_BAD_ARG 1        /* shape / alignment / null pointer (reference: TORCH_CHECKs, mla_bwd.cu:975-1015,1040) */
+#define SMLA_ERR_LAUNCH 2         /* a CUDA runtime or driver call failed (reference prints and ignores, mla_bwd.cu:814-818,965-968) */
+#define SMLA_ERR_WORKSPACE 3      /* workspace too small */
+#define SMLA_ERR_DEVICE_TIMEOUT 4 /* a bounded wait inside a kernel ran out; results are invalid */
+
+/* stages of smla_bwd_run_stages (bit mask) */
+#define SMLA_STAGE_ZERO 1      /* clear dKV                           (reference: torch::zeros, mla_bwd.cu:1027) */
+#define SMLA_STAGE_DELTA 2     /* Delta = rowsum(O * dO)              (reference: preprocess_delta_kernel, mla_bwd.cu:51-95) */
+#define SMLA_STAGE_RECOMPUTE 4 /* S, dS (bf16) from P = QK^T, dP = dO V^T (reference: mla_bwd.cu:225-320, 700-718) */
+#define SMLA_STAGE_DKV 8       /* dKV += S^T dO + dS^T Q, scattered by index (reference: mla_bwd.cu:493-618, 720-753) */
+#define SMLA_STAGE_DQ 16       /* dQ = dS K_gathered                  (reference: mla_bwd.cu:322-404, 729-737) */
+#define SMLA_STAGE_ALL 31
+
+typedef struct smla_bwd_params {
+    /* inputs, all contiguous (reference tensor contract: mla_bwd/mla_bwd.cu:975-1015) */
+    const void* q;          /* bf16 [s_q, h_q, 576] */
+    const void* kv;         /* bf16 [s_kv, 576] */
+    const void* dO;         /* bf16 [s_q, h_q, 512] */
+    const float* lse;       /* f32  [s_q, h_q]  log-sum-exp of the scaled logits */
+    const void* O;          /* bf16 [s_q, h_q, 512] */
+    const int32_t* indices; /* i32  [s_q, topk]; a value outside [0, s_kv) marks an unused slot */
+    /* outputs */
+    void* dQ;               /* bf16 [s_q, h_q, 576], fully overwritten */
+    float* dKV;             /* f32  [s_kv, 576], accumulated into; cleared first when SMLA_STAGE_ZERO runs */
+    int32_t s_q, s_kv, h_q, topk;
+    float sm_scale;          /* <= 0 selects 1/sqrt(576) (reference: mla_bwd/test_mla_bwd.py:38) */
+    int32_t q_start_index_s; /* slot valid only if idx <= q_start_index_s + query row (reference uses 0,
+                                mla_bwd.cu:122,772); SMLA_NO_CAUSAL disables the bound */
+    int32_t lse_is_base2;    /* 1: lse in base-2 units as the reference operator expects (mla_bwd.cu:262-270); 0: natural log */
+} smla_bwd_params;
+
+/* Workspace (device memory) needed for `p`, never more than about `budget_bytes` when that is
+ * non-zero (the query dimension is then processed in several passes).  0 on bad arguments. */
+size_t smla_bwd_workspace_size(const smla_bwd_params* p, size_t budget_bytes);
+
+/* Whole backward: clear dKV, Delta, recompute, dKV, dQ.  `stream` is a cudaStream_t. */
+int smla_bwd_run(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same with a stage mask (SMLA_STAGE_*): lets a caller skip the clear (to accumulate partial
+ * dKV over several calls) and lets tests and profilers run one kernel at a time. */
+int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream,
+                        int stage_mask);
+
+/* Delta only: delta[s_q, h_q] = sum_j O[.., j] * dO[.., j]   (reference: launch_preprocess_delta). */
+int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int32_t h_q, void* stream);
+
+/* Where the pieces of the workspace live, for stage-by-stage checks.  Offsets in bytes. */
+typedef struct smla_bwd_workspace_layout {
+    size_t err_offset;    /* int32 device error word */
+    size_t delta_offset;  /* f32 [s_q, h_q] */
+    size_t s_offset;      /* bf16 [q_chunk, topk_pad, h_pad]  S  of the LAST query chunk processed */
+    size_t ds_offset;     /* bf16 [q_chunk, topk_pad, h_pad]  dS of the LAST query chunk processed */
+    int32_t q_chunk, topk_pad, h_pad;
+    size_t total_bytes;
+} smla_bwd_workspace_layout;
+int smla_bwd_get_workspace_layout(const smla_bwd_params* p, size_t workspace_bytes, smla_bwd_workspace_layout* out);
+
+/* Synchronises `stream`, reads the device error word in the workspace and returns SMLA_OK or
+ * SMLA_ERR_DEVICE_TIMEOUT (or SMLA_ERR_LAUNCH if the stream reports a CUDA error). */
+int smla_bwd_status(void* workspace, void* stream);
+
+/* Number of kernels (own kernels, memset excluded) the last smla_bwd_run_stages on this thread launched. */
+int smla_bwd_last_launch_count(void);
+
+const char* smla_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMLA_BWD_H_ */

@@ -1,0 +1,271 @@
+// C ABI and host launchers of the sparse MLA backward (see include/smla_bwd.h).
+// Host side only: argument checks, workspace carving, TMA descriptor encoding, kernel launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <climits>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/smla_bwd.h"
+#include "smla_kernels.cuh"
+
+namespace {
+
+using smla::KParams;
+
+constexpr size_t kAlign = 256;
+constexpr size_t kDefaultBudget = size_t(6) << 30;  // scratch budget when the caller gives none
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+thread_local int g_last_launches = 0;
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda dependency,
+// so the library also loads on a machine without a driver (symbol checks on a CPU-only box).
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(sym);
+    });
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] with row pitch `pitch_bytes`, box {box_cols, box_rows}, 128-byte swizzle.
+bool make_map_2d(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, uint32_t box_cols,
+                 uint32_t box_rows) {
+    EncodeFn enc = get_encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+struct Plan {
+    int h_pad;       // heads padded to 64 or 128
+    int topk_pad;    // top-k padded to a multiple of 128
+    int q_chunk;     // queries per pass
+    size_t err_off, delta_off, s_off, ds_off, total;
+};
+
+bool check_params(const smla_bwd_params* p) {
+    if (!p) return false;
+    if (p->s_q <= 0 || p->s_kv <= 0 || p->topk <= 0) return false;
+    if (p->h_q <= 0 || p->h_q > 128 || (p->h_q % 8) != 0) return false;
+    // int32 row coordinates in the TMA descriptors
+    if (static_cast<long long>(p->s_q) * p->h_q > INT_MAX) return false;
+    return true;
+}
+
+bool make_plan(const smla_bwd_params* p, size_t budget, Plan* pl) {
+    if (!check_params(p)) return false;
+    pl->h_pad = p->h_q <= 64 ? 64 : 128;
+    pl->topk_pad = (p->topk + 127) / 128 * 128;
+    const size_t per_q = size_t(pl->topk_pad) * pl->h_pad * 2 /*bf16*/ * 2 /*S and dS*/;
+    pl->err_off = 0;
+    pl->delta_off = kAlign;
+    const size_t fixed = align_up(pl->delta_off + size_t(p->s_q) * p->h_q * 4, kAlign);
+    if (budget == 0) budget = kDefaultBudget;
+    size_t qc = budget > fixed ? (budget - fixed) / per_q : 0;
+    if (qc < 1) qc = 1;
+    if (qc > size_t(p->s_q)) qc = p->s_q;
+    // scratch rows are TMA row coordinates (int32)
+    while (qc > 1 && qc * size_t(pl->topk_pad) > size_t(INT_MAX)) qc /= 2;
+    pl->q_chunk = int(qc);
+    pl->s_off = fixed;
+    pl->ds_off = align_up(pl->s_off + qc * per_q / 2, kAlign);
+    pl->total = align_up(pl->ds_off + qc * per_q / 2, kAlign);
+    return true;
+}
+
+// Largest q_chunk that fits a given workspace (layout must match what run() will use).
+bool plan_for_workspace(const smla_bwd_params* p, size_t ws_bytes, Plan* pl) {
+    if (!make_plan(p, ws_bytes, pl)) return false;
+    while (pl->total > ws_bytes && pl->q_chunk > 1) {
+        Plan t = *pl;
+        const size_t per_q = size_t(pl->topk_pad) * pl->h_pad * 4;
+        size_t over = pl->total - ws_bytes;
+        int dec = int(over / per_q) + 1;
+        t.q_chunk = pl->q_chunk - dec < 1 ? 1 : pl->q_chunk - dec;
+        t.ds_off = align_up(t.s_off + size_t(t.q_chunk) * per_q / 2, kAlign);
+        t.total = align_up(t.ds_off + size_t(t.q_chunk) * per_q / 2, kAlign);
+        *pl = t;
+    }
+    return pl->total <= ws_bytes;
+}
+
+template <typename K>
+bool set_smem(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+template <int HP>
+int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages) {
+    using namespace smla;
+    __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
+    __nv_bfloat16* ds_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.ds_off);
+    float* delta = reinterpret_cast<float*>(ws + pl.delta_off);
+
+    CUtensorMap tm_q64, tm_do64, tm_qhp, tm_dohp, tm_kv, tm_s, tm_ds;
+    const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
+    const uint64_t srows = uint64_t(pl.q_chunk) * pl.topk_pad;
+    bool ok = true;
+    ok &= make_map_2d(&tm_q64, p->q, kDQK, qrows, kDQK * 2, 64, 64);
+    ok &= make_map_2d(&tm_do64, p->dO, kDV, qrows, kDV * 2, 64, 64);
+    ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
+    ok &= make_map_2d(&tm_dohp, p->dO, kDV, qrows, kDV * 2, 64, HP);
+    ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
+    ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
+    ok &= make_map_2d(&tm_ds, ds_scr, HP, srows, HP * 2, 64, 64);
+    if (!ok) return SMLA_ERR_LAUNCH;
+
+    // per device, so set on every call (cheap) rather than once per process
+    bool attr_ok = set_smem(smla_recompute_kernel<HP>, rc::kSmemBytes);
+    attr_ok &= set_smem(smla_dkv_kernel<HP>, dk::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_dq_kernel<HP>, dq::Cfg<HP>::kSmemBytes);
+    if (!attr_ok) return SMLA_ERR_LAUNCH;
+
+    KParams kp{};
+    kp.indices = p->indices;
+    kp.lse = p->lse;
+    kp.delta = delta;
+    kp.s_scr = s_scr;
+    kp.ds_scr = ds_scr;
+    kp.dKV = p->dKV;
+    kp.dQ = reinterpret_cast<__nv_bfloat16*>(p->dQ);
+    kp.g_err = reinterpret_cast<int*>(ws + pl.err_off);
+    kp.s_q = p->s_q;
+    kp.s_kv = p->s_kv;
+    kp.h_q = p->h_q;
+    kp.topk = p->topk;
+    kp.topk_pad = pl.topk_pad;
+    kp.sm_scale = p->sm_scale > 0.f ? p->sm_scale : 1.0f / sqrtf(float(kDQK));
+    kp.scale_log2e = kp.sm_scale * 1.4426950408889634f;
+    kp.lse_mult = p->lse_is_base2 ? 1.0f : 1.4426950408889634f;
+    kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
+    kp.q_start = kp.causal ? p->q_start_index_s : 0;
+
+    if (stages & SMLA_STAGE_DELTA) {
+        const int n_rows = p->s_q * p->h_q;
+        smla_delta_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(reinterpret_cast<const uint4*>(p->O),
+                                                          reinterpret_cast<const uint4*>(p->dO), delta, n_rows);
+        ++g_last_launches;
+    }
+    for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
+        const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
+        kp.q0 = q0;
+        if (stages & SMLA_STAGE_RECOMPUTE) {
+            smla_recompute_kernel<HP><<<nq * (HP / 64), rc::kThreads, rc::kSmemBytes, st>>>(tm_q64, tm_do64, tm_kv, kp);
+            ++g_last_launches;
+        }
+        if (stages & SMLA_STAGE_DKV) {
+            smla_dkv_kernel<HP><<<nq * 2, dk::kThreads, dk::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
+            ++g_last_launches;
+        }
+        if (stages & SMLA_STAGE_DQ) {
+            smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_ds, kp);
+            ++g_last_launches;
+        }
+    }
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+size_t smla_bwd_workspace_size(const smla_bwd_params* p, size_t budget_bytes) {
+    Plan pl;
+    if (!make_plan(p, budget_bytes, &pl)) return 0;
+    return pl.total;
+}
+
+int smla_bwd_get_workspace_layout(const smla_bwd_params* p, size_t workspace_bytes, smla_bwd_workspace_layout* out) {
+    Plan pl;
+    if (!out || !check_params(p)) return SMLA_ERR_BAD_ARG;
+    if (!plan_for_workspace(p, workspace_bytes, &pl)) return SMLA_ERR_WORKSPACE;
+    out->err_offset = pl.err_off;
+    out->delta_offset = pl.delta_off;
+    out->s_offset = pl.s_off;
+    out->ds_offset = pl.ds_off;
+    out->q_chunk = pl.q_chunk;
+    out->topk_pad = pl.topk_pad;
+    out->h_pad = pl.h_pad;
+    out->total_bytes = pl.total;
+    return SMLA_OK;
+}
+
+int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream, int stage_mask) {
+    g_last_launches = 0;
+    if (!check_params(p) || !workspace) return SMLA_ERR_BAD_ARG;
+    if (!p->q || !p->kv || !p->dO || !p->lse || !p->O || !p->indices || !p->dQ || !p->dKV) return SMLA_ERR_BAD_ARG;
+    // TMA needs 16-byte aligned bases; vector loads/stores need the same for the rest
+    if (!aligned16(p->q) || !aligned16(p->kv) || !aligned16(p->dO) || !aligned16(p->O) || !aligned16(p->dQ) ||
+        !aligned16(p->dKV) || (reinterpret_cast<uintptr_t>(workspace) & (kAlign - 1)))
+        return SMLA_ERR_BAD_ARG;
+    Plan pl;
+    if (!plan_for_workspace(p, workspace_bytes, &pl)) return SMLA_ERR_WORKSPACE;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    if (cudaMemsetAsync(ws + pl.err_off, 0, 4, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
+    if (stage_mask & SMLA_STAGE_ZERO) {
+        if (cudaMemsetAsync(p->dKV, 0, size_t(p->s_kv) * SMLA_D_QK * sizeof(float), st) != cudaSuccess)
+            return SMLA_ERR_LAUNCH;
+    }
+    return pl.h_pad == 64 ? launch_chain<64>(p, pl, ws, st, stage_mask) : launch_chain<128>(p, pl, ws, st, stage_mask);
+}
+
+int smla_bwd_run(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+    return smla_bwd_run_stages(p, workspace, workspace_bytes, stream, SMLA_STAGE_ALL);
+}
+
+int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int32_t h_q, void* stream) {
+    if (!O || !dO || !delta || s_q <= 0 || h_q <= 0 || !aligned16(O) || !aligned16(dO)) return SMLA_ERR_BAD_ARG;
+    if (static_cast<long long>(s_q) * h_q > INT_MAX) return SMLA_ERR_BAD_ARG;
+    const int n_rows = s_q * h_q;
+    smla::smla_delta_kernel<<<(n_rows + 7) / 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(O), reinterpret_cast<const uint4*>(dO), delta, n_rows);
+    g_last_launches = 1;
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
+
+int smla_bwd_status(void* workspace, void* stream) {
+    if (!workspace) return SMLA_ERR_BAD_ARG;
+    int flag = 0;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&flag, workspace, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return SMLA_ERR_LAUNCH;
+    return flag == 0 ? SMLA_OK : SMLA_ERR_DEVICE_TIMEOUT;
+}
+
+int smla_bwd_last_launch_count(void) { return g_last_launches; }
+
+const char* smla_status_string(int status) {
+    switch (status) {
+        case SMLA_OK: return "ok";
+        case SMLA_ERR_BAD_ARG: return "bad argument (null/misaligned pointer or unsupported shape)";
+        case SMLA_ERR_LAUNCH: return "CUDA launch or driver call failed";
+        case SMLA_ERR_WORKSPACE: return "workspace too small";
+        case SMLA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out; results are invalid";
+        default: return "unknown status";
+    }
+}
+
+}  // extern "C"

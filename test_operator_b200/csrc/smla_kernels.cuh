@@ -1,0 +1,600 @@
+// Device kernels of the sparse MLA backward for sm_100a.
+//
+// The backward of one query token is a chain of five contractions around a softmax-gradient
+// step.  It is split into four kernels that hand bf16 S / dS through a scratch buffer:
+//
+//   delta      Delta[q,h] = sum_j O[q,h,j] * dO[q,h,j]                         (HBM-bound)
+//   recompute  P^T = K_g Q^T, dP^T = V_g dO^T  (tcgen05, keys on the M axis),
+//              S = exp2(P*scale*log2e - lse), dS = S*(dP - Delta)*scale -> bf16 scratch
+//   dkv        dKV^T[d, key] = dO^T S + Q^T dS (tcgen05, d on the M axis), then one coalesced
+//              fp32 reduction per (key, 32 consecutive d) straight from TMEM registers
+//   dq         dQ^T[d, head] = K_g^T dS^T (tcgen05, d on the M axis) accumulated over all keys
+//
+// Heads are always on the N or K axis of the MMAs, so h_q = 16 / 64 / 128 use the same code
+// (HP = heads padded to 64 or 128).  All shared-memory operand tiles are 128-byte-swizzled
+// [rows x 64 bf16] chunks written by TMA; a chunk is read K-major or MN-major by choosing the
+// descriptor, never by moving data.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "sm100_ptx.cuh"
+
+namespace smla {
+
+constexpr int kDQK = 576;
+constexpr int kDV = 512;
+constexpr int kQChunks = kDQK / 64;   // 9 column chunks of 64
+constexpr int kVChunks = kDV / 64;    // 8
+constexpr int kSplitChunk = 5;        // d-part 0 = chunks [0,5) = columns [0,320); part 1 = chunks [5,9)
+
+struct KParams {
+    const int32_t* indices;   // [s_q, topk]
+    const float* lse;         // [s_q, h_q]
+    const float* delta;       // [s_q, h_q]
+    __nv_bfloat16* s_scr;     // [q_chunk, topk_pad, HP]
+    __nv_bfloat16* ds_scr;    // [q_chunk, topk_pad, HP]
+    float* dKV;               // [s_kv, 576]
+    __nv_bfloat16* dQ;        // [s_q, h_q, 576]
+    int* g_err;
+    int q0;                   // first query (global row) of this pass
+    int s_q, s_kv, h_q, topk, topk_pad;
+    float sm_scale, scale_log2e, lse_mult;
+    int q_start, causal;
+};
+
+// error codes recorded by bounded waits: 100*kernel + site
+enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300 };
+
+__device__ __forceinline__ bool slot_valid(int idx, int q_global, const KParams& p) {
+    return idx >= 0 && idx < p.s_kv && (!p.causal || idx <= p.q_start + q_global);
+}
+
+// =============================================================================================
+// Delta = rowsum(O * dO).  One warp per (query, head) row of 512 bf16; each lane reads 2 x 16 B
+// of each tensor, so a warp reads 2 x 1 KB fully coalesced.
+// =============================================================================================
+__global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO,
+                                                         float* __restrict__ delta, int n_rows) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const uint4* o = O + static_cast<size_t>(row) * (kDV / 8);
+    const uint4* g = dO + static_cast<size_t>(row) * (kDV / 8);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 a = __ldg(o + lane + 32 * i);
+        uint4 b = __ldg(g + lane + 32 * i);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 x = __bfloat1622float2(pa[k]);
+            float2 y = __bfloat1622float2(pb[k]);
+            acc = fmaf(x.x, y.x, acc);
+            acc = fmaf(x.y, y.y, acc);
+        }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) delta[row] = acc;
+}
+
+// =============================================================================================
+// recompute: one CTA per (query, group of 64 heads).
+//   warp 0      producer: Q / dO chunks of its head group once (TMA tiled), then per 128-key tile
+//               nine [128 keys x 64 col] chunks of gathered kv rows (TMA gather4, 4 rows per lane)
+//   warp 1      UMMA issuer: P^T[128 keys, 64 heads] += Kg_chunk . Q_chunk^T  (9 chunks, K = 576)
+//                            dP^T                    += Kg_chunk . dO_chunk^T (8 chunks, K = 512)
+//               accumulators double-buffered in TMEM (2 x 128 columns)
+//   warps 2-5   softmax-gradient: thread = key row; reads P^T, dP^T from TMEM, writes one 128-byte
+//               row of S and of dS (bf16) to the scratch
+// =============================================================================================
+namespace rc {
+constexpr int kThreads = 192;
+constexpr int kStages = 5;
+constexpr int kTileKeys = 128;
+constexpr int kChunkBytesA = kTileKeys * 128;  // 16 KB gathered chunk
+constexpr int kChunkBytesB = 64 * 128;         // 8 KB Q / dO chunk (64 heads)
+constexpr int kOffQ = 0;
+constexpr int kOffDO = kOffQ + kQChunks * kChunkBytesB;
+constexpr int kOffRing = kOffDO + kVChunks * kChunkBytesB;
+constexpr int kOffMisc = kOffRing + kStages * kChunkBytesA;
+constexpr int kSmemBytes = kOffMisc + 1024 + 1024;  // + misc + alignment slack
+}  // namespace rc
+
+template <int HP>
+__global__ void __launch_bounds__(rc::kThreads, 1)
+smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_kv, const KParams p) {
+    using namespace rc;
+    constexpr int G = HP / 64;
+    const int g = blockIdx.x % G;
+    const int ql = blockIdx.x / G;
+    const int qg = p.q0 + ql;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t s_base = smem_u32(smem);
+    uint8_t* misc = smem + kOffMisc;
+    // misc: [0,512) lse2[64] + delta[64]; [512, ...) barriers; tmem ptr; abort flag
+    float* lse_s = reinterpret_cast<float*>(misc);
+    float* delta_s = lse_s + 64;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 512);
+    const uint32_t bar_full = smem_u32(bars);                  // [kStages]
+    const uint32_t bar_empty = bar_full + 8 * kStages;         // [kStages]
+    const uint32_t bar_qdo = bar_empty + 8 * kStages;          // 1
+    const uint32_t bar_tfull = bar_qdo + 8;                    // [2]
+    const uint32_t bar_tempty = bar_tfull + 16;                // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 512 + 8 * (2 * kStages + 5));
+    volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const WaitCtx wc{p.g_err, s_abort};
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        mbar_init(bar_qdo, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + 8 * i, 1);
+            mbar_init(bar_tempty + 8 * i, 4);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int n_tiles = p.topk_pad / kTileKeys;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_do);
+            tma_prefetch_desc(&tm_kv);
+            mbar_arrive_expect_tx(bar_qdo, (kQChunks + kVChunks) * kChunkBytesB);
+            const int row0 = qg * p.h_q + 64 * g;
+            for (int j = 0; j < kQChunks; ++j) tma_load_2d(s_base + kOffQ + j * kChunkBytesB, &tm_q, 64 * j, row0, bar_qdo);
+            for (int j = 0; j < kVChunks; ++j) tma_load_2d(s_base + kOffDO + j * kChunkBytesB, &tm_do, 64 * j, row0, bar_qdo);
+        }
+        int it = 0;
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            int r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int key = tile * kTileKeys + lane * 4 + k;
+                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                r[k] = min(max(idx, 0), p.s_kv - 1);  // unused slots gather a real row; their S, dS are forced to 0
+            }
+            for (int j = 0; j < kQChunks; ++j, ++it) {
+                const int s = it % kStages;
+                const uint32_t ph = (it / kStages) & 1;
+                mbar_wait(bar_empty + 8 * s, ph ^ 1, wc, kErrRecompute + 1);
+                if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, kChunkBytesA);
+                __syncwarp();
+                tma_gather4(s_base + kOffRing + s * kChunkBytesA + lane * 512, &tm_kv, 64 * j, r[0], r[1], r[2], r[3],
+                            bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(128, 64, 0, 0);
+            mbar_wait(bar_qdo, 0, wc, kErrRecompute + 2);
+            int it = 0;
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const int b = tile & 1;
+                mbar_wait(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 3);
+                tc_fence_after_sync();
+                const uint32_t d_p = tmem + b * 128;
+                const uint32_t d_dp = d_p + 64;
+                for (int j = 0; j < kQChunks; ++j, ++it) {
+                    const int s = it % kStages;
+                    mbar_wait(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 4);
+                    tc_fence_after_sync();
+                    const uint32_t a0 = s_base + kOffRing + s * kChunkBytesA;
+                    const uint32_t bq = s_base + kOffQ + j * kChunkBytesB;
+                    const uint32_t bd = s_base + kOffDO + j * kChunkBytesB;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t ad = make_smem_desc(a0 + 32 * k, 16, 1024, kSwizzle128);
+                        umma_ss(d_p, ad, make_smem_desc(bq + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
+                        if (j < kVChunks)
+                            umma_ss(d_dp, ad, make_smem_desc(bd + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
+                    }
+                    umma_commit(bar_empty + 8 * s);
+                }
+                umma_commit(bar_tfull + 8 * b);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax gradient
+        const int quarter = warp & 3;
+        const int st = threadIdx.x - 64;  // 0..127
+        if (st < 64) {
+            const int h = 64 * g + st;
+            const bool hv = h < p.h_q;
+            lse_s[st] = hv ? p.lse[static_cast<size_t>(qg) * p.h_q + h] * p.lse_mult : __int_as_float(0x7f800000);
+            delta_s[st] = hv ? p.delta[static_cast<size_t>(qg) * p.h_q + h] : 0.f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int row = quarter * 32 + lane;
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const int key = tile * kTileKeys + row;
+            const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+            const bool valid = slot_valid(idx, qg, p);
+            const int b = tile & 1;
+            mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 5);
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * 128;
+            const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + 64 * g;
+            uint4* s_out = reinterpret_cast<uint4*>(p.s_scr + off);
+            uint4* ds_out = reinterpret_cast<uint4*>(p.ds_scr + off);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t pv[32], dpv[32];
+                tmem_ld_32x32(taddr + half * 32, pv);
+                tmem_ld_32x32(taddr + 64 + half * 32, dpv);
+                tmem_ld_wait();
+                uint32_t so[16], dso[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    float sv[2], dsv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int h = half * 32 + c + e;
+                        const float s = valid ? ex2_approx(fmaf(__uint_as_float(pv[c + e]), p.scale_log2e, -lse_s[h])) : 0.f;
+                        sv[e] = s;
+                        dsv[e] = valid ? s * (__uint_as_float(dpv[c + e]) - delta_s[h]) * p.sm_scale : 0.f;
+                    }
+                    so[c >> 1] = pack_bf16x2(sv[0], sv[1]);
+                    dso[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+                }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    s_out[half * 4 + v] = make_uint4(so[4 * v], so[4 * v + 1], so[4 * v + 2], so[4 * v + 3]);
+                    ds_out[half * 4 + v] = make_uint4(dso[4 * v], dso[4 * v + 1], dso[4 * v + 2], dso[4 * v + 3]);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+// =============================================================================================
+// dkv: one CTA per (query, d-part).  d-part 0 owns columns [0,320), part 1 owns [320,576).
+//   resident   Q^T and dO^T of the part: chunks [HP heads x 64 d] read MN-major as the A operand
+//              (M = d, 128 rows = two adjacent chunks, K = heads)
+//   warp 0     producer: resident chunks once, then per 64-key tile the S and dS scratch tiles
+//              [64 keys x HP heads] (B operand, K-major)
+//   warp 1     UMMA issuer: acc[blk][128 d, 64 keys] = dO^T . S + Q^T . dS, double-buffered in TMEM
+//   warps 2-5  drain: thread = d row; one fp32 reduction per key, 32 lanes -> 128 contiguous bytes
+// Part 0's third block has 64 real rows (d 256..319); its upper 64 rows read whatever follows
+// in shared memory and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
+// =============================================================================================
+namespace dk {
+constexpr int kThreads = 192;
+constexpr int kTileKeys = 64;
+constexpr int kResChunks = 5;
+template <int HP> struct Cfg {
+    static constexpr int kChunk = HP * 128;                 // resident chunk bytes
+    static constexpr int kTileMat = (HP / 64) * 8192;       // one S (or dS) tile
+    static constexpr int kStage = 2 * kTileMat;
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffDO = kResChunks * kChunk;
+    static constexpr int kOffStage = 2 * kResChunks * kChunk;
+    static constexpr int kOffMisc = kOffStage + 2 * kStage;
+    static constexpr int kSmemBytes = kOffMisc + 256 + 1024;
+    static constexpr int kAccCols = 192;                    // 3 blocks x 64 keys per buffer
+};
+}  // namespace dk
+
+template <int HP>
+__global__ void __launch_bounds__(dk::kThreads, 1)
+smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
+    using namespace dk;
+    using C = Cfg<HP>;
+    const int part = blockIdx.x & 1;
+    const int ql = blockIdx.x >> 1;
+    const int qg = p.q0 + ql;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_blk = part ? 2 : 3;
+    const int chunk0 = part ? kSplitChunk : 0;
+    const int n_q = part ? kQChunks - kSplitChunk : kSplitChunk;           // 4 : 5
+    const int n_do = part ? kVChunks - kSplitChunk : kSplitChunk;          // 3 : 5 (real dO chunks)
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t s_base = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffMisc);
+    const uint32_t bar_full = smem_u32(bars);      // [2]
+    const uint32_t bar_empty = bar_full + 16;      // [2]
+    const uint32_t bar_res = bar_empty + 16;       // 1
+    const uint32_t bar_afull = bar_res + 8;        // [2]
+    const uint32_t bar_aempty = bar_afull + 16;    // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 80);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const WaitCtx wc{p.g_err, s_abort};
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+            mbar_init(bar_afull + 8 * i, 1);
+            mbar_init(bar_aempty + 8 * i, 4);
+        }
+        mbar_init(bar_res, 1);
+        fence_mbar_init();
+    }
+    if (part == 1) {  // zero chunk standing in for dO columns 512..575
+        uint4* z = reinterpret_cast<uint4*>(smem + C::kOffDO + n_do * C::kChunk);
+        for (int i = threadIdx.x; i < C::kChunk / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int n_tiles = p.topk_pad / kTileKeys;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_do);
+            tma_prefetch_desc(&tm_s);
+            tma_prefetch_desc(&tm_ds);
+            mbar_arrive_expect_tx(bar_res, (n_q + n_do) * C::kChunk);
+            const int row0 = qg * p.h_q;
+            for (int j = 0; j < n_q; ++j)
+                tma_load_2d(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * (chunk0 + j), row0, bar_res);
+            for (int j = 0; j < n_do; ++j)
+                tma_load_2d(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res);
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const int s = tile & 1;
+                mbar_wait(bar_empty + 8 * s, ((tile >> 1) & 1) ^ 1, wc, kErrDkv + 1);
+                mbar_arrive_expect_tx(bar_full + 8 * s, C::kStage);
+                const int row = ql * p.topk_pad + tile * kTileKeys;
+                const uint32_t dst = s_base + C::kOffStage + s * C::kStage;
+                for (int c = 0; c < HP / 64; ++c) {
+                    tma_load_2d(dst + c * 8192, &tm_s, 64 * c, row, bar_full + 8 * s);
+                    tma_load_2d(dst + C::kTileMat + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 0);  // A MN-major (d contiguous), B K-major
+            mbar_wait(bar_res, 0, wc, kErrDkv + 2);
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const int s = tile & 1;
+                const uint32_t ph = (tile >> 1) & 1;
+                mbar_wait(bar_aempty + 8 * s, ph ^ 1, wc, kErrDkv + 3);
+                mbar_wait(bar_full + 8 * s, ph, wc, kErrDkv + 4);
+                tc_fence_after_sync();
+                const uint32_t st_s = s_base + C::kOffStage + s * C::kStage;
+                const uint32_t st_ds = st_s + C::kTileMat;
+                for (int blk = 0; blk < n_blk; ++blk) {
+                    const uint32_t d = tmem + s * C::kAccCols + blk * 64;
+                    const uint32_t a_do = s_base + C::kOffDO + 2 * blk * C::kChunk;
+                    const uint32_t a_q = s_base + C::kOffQ + 2 * blk * C::kChunk;
+#pragma unroll
+                    for (int ks = 0; ks < HP / 16; ++ks)
+                        umma_ss(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
+                                make_smem_desc(st_s + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
+                                ks != 0);
+#pragma unroll
+                    for (int ks = 0; ks < HP / 16; ++ks)
+                        umma_ss(d, make_smem_desc(a_q + ks * 2048, C::kChunk, 1024, kSwizzle128),
+                                make_smem_desc(st_ds + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
+                                1);
+                }
+                umma_commit(bar_empty + 8 * s);
+                umma_commit(bar_afull + 8 * s);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int d_part0 = chunk0 * 64;
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const int s = tile & 1;
+            int idx2[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = tile * kTileKeys + 32 * e + lane;
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                idx2[e] = slot_valid(idx, qg, p) ? idx : -1;
+            }
+            mbar_wait(bar_afull + 8 * s, (tile >> 1) & 1, wc, kErrDkv + 5);
+            tc_fence_after_sync();
+            for (int blk = 0; blk < n_blk; ++blk) {
+                if (part == 0 && blk == 2 && quarter >= 2) continue;  // padded rows
+                float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane;
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + s * C::kAccCols + blk * 64;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + 32 * e, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int idx = __shfl_sync(0xffffffffu, idx2[e], j);
+                        if (idx >= 0) red_add_f32(out + static_cast<size_t>(idx) * kDQK, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_aempty + 8 * s);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// =============================================================================================
+// dq: one CTA per (query, d-part); same d split as dkv.
+//   warp 0     producer: per 64-key tile the dS scratch tile [64 keys x HP heads] (TMA tiled) and
+//              the part's columns of the gathered kv rows (TMA gather4, lanes 0-15 x 4 rows)
+//   warp 1     UMMA issuer: acc[blk][128 d, HP heads] += Kg^T . dS^T  (both operands MN-major:
+//              the key index is the contraction and runs along shared-memory rows)
+//   warps 2-5  epilogue: TMEM -> bf16 -> dQ[q, head, d]
+// =============================================================================================
+namespace dq {
+constexpr int kThreads = 192;
+constexpr int kTileKeys = 64;
+constexpr int kStages = 3;
+template <int HP> struct Cfg {
+    static constexpr int kKgBytes = 5 * 8192;
+    static constexpr int kDsBytes = (HP / 64) * 8192;
+    static constexpr int kStage = kKgBytes + kDsBytes;     // dS right after Kg: block 2's padded rows read dS
+    static constexpr int kOffMisc = kStages * kStage;
+    static constexpr int kSmemBytes = kOffMisc + 256 + 1024;
+    static constexpr int kTmemCols = HP == 128 ? 512 : 256;
+};
+}  // namespace dq
+
+template <int HP>
+__global__ void __launch_bounds__(dq::kThreads, 1)
+smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
+    using namespace dq;
+    using C = Cfg<HP>;
+    const int part = blockIdx.x & 1;
+    const int ql = blockIdx.x >> 1;
+    const int qg = p.q0 + ql;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_blk = part ? 2 : 3;
+    const int chunk0 = part ? kSplitChunk : 0;
+    const int n_ch = part ? kQChunks - kSplitChunk : kSplitChunk;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t s_base = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffMisc);
+    const uint32_t bar_full = smem_u32(bars);             // [kStages]
+    const uint32_t bar_empty = bar_full + 8 * kStages;    // [kStages]
+    const uint32_t bar_acc = bar_empty + 8 * kStages;     // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (2 * kStages + 1));
+    volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const WaitCtx wc{p.g_err, s_abort};
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        mbar_init(bar_acc, 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int n_tiles = p.topk_pad / kTileKeys;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_kv);
+            tma_prefetch_desc(&tm_ds);
+        }
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const int s = tile % kStages;
+            int r[4] = {0, 0, 0, 0};
+            if (lane < 16) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int key = tile * kTileKeys + lane * 4 + k;
+                    int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                    r[k] = min(max(idx, 0), p.s_kv - 1);
+                }
+            }
+            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1);
+            const uint32_t dst = s_base + s * C::kStage;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar_full + 8 * s, n_ch * 8192 + C::kDsBytes);
+                const int row = ql * p.topk_pad + tile * kTileKeys;
+                for (int c = 0; c < HP / 64; ++c) tma_load_2d(dst + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
+            }
+            __syncwarp();
+            if (lane < 16) {
+                for (int c = 0; c < n_ch; ++c)
+                    tma_gather4(dst + c * 8192 + lane * 512, &tm_kv, 64 * (chunk0 + c), r[0], r[1], r[2], r[3],
+                                bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(128, HP, 1, 1);
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const int s = tile % kStages;
+                mbar_wait(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
+                tc_fence_after_sync();
+                const uint32_t kg = s_base + s * C::kStage;
+                const uint32_t ds = kg + C::kKgBytes;
+                for (int blk = 0; blk < n_blk; ++blk) {
+#pragma unroll
+                    for (int ks = 0; ks < kTileKeys / 16; ++ks)
+                        umma_ss(tmem + blk * HP, make_smem_desc(kg + 2 * blk * 8192 + ks * 2048, 8192, 1024, kSwizzle128),
+                                make_smem_desc(ds + ks * 2048, 8192, 1024, kSwizzle128), idesc, (tile | ks) != 0);
+                }
+                umma_commit(bar_empty + 8 * s);
+            }
+            umma_commit(bar_acc);
+        }
+    } else {
+        const int quarter = warp & 3;
+        mbar_wait(bar_acc, 0, wc, kErrDq + 3);
+        tc_fence_after_sync();
+        for (int blk = 0; blk < n_blk; ++blk) {
+            if (part == 0 && blk == 2 && quarter >= 2) continue;
+            const int d = chunk0 * 64 + blk * 128 + quarter * 32 + lane;
+            __nv_bfloat16* out = p.dQ + static_cast<size_t>(qg) * p.h_q * kDQK + d;
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + blk * HP;
+#pragma unroll 1
+            for (int cb = 0; cb < HP / 32; ++cb) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + cb * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int h = cb * 32 + j;
+                    if (h < p.h_q) out[static_cast<size_t>(h) * kDQK] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, C::kTmemCols);
+}
+
+}  // namespace smla

@@ -1,0 +1,248 @@
+"""Host-side mirror of the reference operator `mla_bwd_cuda.mla_bwd` over the C-ABI library.
+
+Reference surface: `mla_bwd(q, kv, dO, lse, O, indices) -> (dQ, dKV)` (`mla_bwd/mla_bwd.cu:972-1063`,
+called positionally by `mla_bwd/test_mla_bwd.py:103,140`).  Same positional order and the same
+checks / error behaviour (`RuntimeError` for shape, dtype, device and contiguity problems); the
+trailing keyword arguments are additions.  torch is used only for device memory and the current
+stream; all arithmetic happens in the hand-written CUDA kernels behind `include/smla_bwd.h`.
+There is no CPU or eager fallback: if the library is missing and cannot be built, import fails.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+from . import build as _build
+
+D_QK = 576
+D_V = 512
+NO_CAUSAL = -(2 ** 31)
+
+STAGE_ZERO, STAGE_DELTA, STAGE_RECOMPUTE, STAGE_DKV, STAGE_DQ = 1, 2, 4, 8, 16
+STAGE_ALL = 31
+
+
+class _Params(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("kv", ctypes.c_void_p), ("dO", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("O", ctypes.c_void_p), ("indices", ctypes.c_void_p), ("dQ", ctypes.c_void_p), ("dKV", ctypes.c_void_p),
+        ("s_q", ctypes.c_int32), ("s_kv", ctypes.c_int32), ("h_q", ctypes.c_int32), ("topk", ctypes.c_int32),
+        ("sm_scale", ctypes.c_float), ("q_start_index_s", ctypes.c_int32), ("lse_is_base2", ctypes.c_int32),
+    ]
+
+
+class WorkspaceLayout(ctypes.Structure):
+    _fields_ = [
+        ("err_offset", ctypes.c_size_t), ("delta_offset", ctypes.c_size_t), ("s_offset", ctypes.c_size_t),
+        ("ds_offset", ctypes.c_size_t), ("q_chunk", ctypes.c_int32), ("topk_pad", ctypes.c_int32),
+        ("h_pad", ctypes.c_int32), ("total_bytes", ctypes.c_size_t),
+    ]
+
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def load_library() -> ctypes.CDLL:
+    """Load (building first if the sources are newer) the C-ABI shared library."""
+    global _lib
+    with _lib_lock:
+        if _lib is not None:
+            return _lib
+        path = _build.LIB_PATH
+        if _build.needs_build():
+            try:
+                _build.build()
+            except Exception as e:  # prebuilt library on a box without nvcc is fine; none at all is not
+                if not os.path.exists(path):
+                    raise RuntimeError(f"sparse MLA CUDA library is missing and could not be built: {e}") from e
+        lib = ctypes.CDLL(path)
+        lib.smla_bwd_workspace_size.restype = ctypes.c_size_t
+        lib.smla_bwd_workspace_size.argtypes = [ctypes.POINTER(_Params), ctypes.c_size_t]
+        lib.smla_bwd_run.restype = ctypes.c_int
+        lib.smla_bwd_run.argtypes = [ctypes.POINTER(_Params), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        lib.smla_bwd_run_stages.restype = ctypes.c_int
+        lib.smla_bwd_run_stages.argtypes = [ctypes.POINTER(_Params), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+                                            ctypes.c_int]
+        lib.smla_bwd_delta.restype = ctypes.c_int
+        lib.smla_bwd_delta.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                       ctypes.c_int32, ctypes.c_void_p]
+        lib.smla_bwd_get_workspace_layout.restype = ctypes.c_int
+        lib.smla_bwd_get_workspace_layout.argtypes = [ctypes.POINTER(_Params), ctypes.c_size_t,
+                                                      ctypes.POINTER(WorkspaceLayout)]
+        lib.smla_bwd_status.restype = ctypes.c_int
+        lib.smla_bwd_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.smla_bwd_last_launch_count.restype = ctypes.c_int
+        lib.smla_bwd_status_string = lib.smla_status_string
+        lib.smla_status_string.restype = ctypes.c_char_p
+        lib.smla_status_string.argtypes = [ctypes.c_int]
+        _lib = lib
+        return lib
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _raise_status(lib, status: int, what: str) -> None:
+    if status != 0:
+        raise RuntimeError(f"{what}: {lib.smla_status_string(status).decode()} (status {status})")
+
+
+class Workspace:
+    """Device scratch owned by the caller (delta, bf16 S / dS, error word); reusable across calls."""
+
+    def __init__(self, nbytes: int, device):
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.nbytes = nbytes
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr()
+
+
+def _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV2, sm_scale, q_start_index_s, lse_is_base2) -> _Params:
+    return _Params(
+        q.data_ptr(), kv2.data_ptr(), dO.data_ptr(), lse.data_ptr(), O.data_ptr(), idx2.data_ptr(),
+        dQ.data_ptr(), dKV2.data_ptr(),
+        q.shape[0], kv2.shape[0], q.shape[1], idx2.shape[1],
+        float(sm_scale) if sm_scale is not None else 0.0,
+        NO_CAUSAL if q_start_index_s is None else int(q_start_index_s),
+        1 if lse_is_base2 else 0,
+    )
+
+
+def _validate(q, kv, dO, lse, O, indices):
+    """The reference's TORCH_CHECKs (`mla_bwd/mla_bwd.cu:975-1015`), widened to h_q in {8..128} and 3-D kv/indices."""
+    for name, t in (("q", q), ("kv", kv), ("dO", dO), ("lse", lse), ("O", O), ("indices", indices)):
+        _check(isinstance(t, torch.Tensor), f"{name} must be a tensor")
+        _check(t.is_cuda, f"{name} must be a CUDA tensor")
+        _check(t.is_contiguous(), f"{name} must be contiguous")
+        _check(t.device == q.device, f"{name} must be on the same device as q")
+    _check(q.dtype == torch.bfloat16, "q must be bfloat16")
+    _check(kv.dtype == torch.bfloat16, "kv must be bfloat16")
+    _check(dO.dtype == torch.bfloat16, "dO must be bfloat16")
+    _check(O.dtype == torch.bfloat16, "O must be bfloat16")
+    _check(lse.dtype == torch.float32, "lse must be float32")
+    _check(indices.dtype == torch.int32, "indices must be int32")
+    _check(q.dim() == 3, "q must have shape [s_q, h_q, 576]")
+    _check(kv.dim() in (2, 3), "kv must have shape [s_kv, 576] or [s_kv, 1, 576]")
+    _check(indices.dim() in (2, 3), "indices must have shape [s_q, topk] or [s_q, 1, topk]")
+    if kv.dim() == 3:
+        _check(kv.shape[1] == 1, "only h_kv = 1 is supported")
+    if indices.dim() == 3:
+        _check(indices.shape[1] == 1, "only h_kv = 1 is supported")
+    s_q, h_q, d_qk = q.shape
+    _check(d_qk == D_QK, f"q last dim must be {D_QK}")
+    _check(kv.shape[-1] == D_QK, f"kv last dim must be {D_QK}")
+    _check(0 < h_q <= 128 and h_q % 8 == 0, f"h_q must be a multiple of 8 in [8, 128], got {h_q}")
+    _check(tuple(dO.shape) == (s_q, h_q, D_V), f"dO must have shape [{s_q}, {h_q}, {D_V}]")
+    _check(tuple(O.shape) == (s_q, h_q, D_V), f"O must have shape [{s_q}, {h_q}, {D_V}]")
+    _check(tuple(lse.shape) == (s_q, h_q), f"lse must have shape [{s_q}, {h_q}]")
+    _check(indices.shape[0] == s_q, "indices first dim must equal s_q")
+    topk = indices.shape[-1]
+    _check(topk > 0, "topk must be positive")
+
+
+def mla_bwd(
+    q: torch.Tensor, kv: torch.Tensor, dO: torch.Tensor, lse: torch.Tensor, O: torch.Tensor, indices: torch.Tensor,
+    sm_scale: Optional[float] = None,
+    q_start_index_s: Optional[int] = 0,
+    lse_is_base2: bool = True,
+    out_dkv: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    workspace: Optional[Workspace] = None,
+    workspace_budget: int = 0,
+    check_device_status: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sparse MLA attention backward.  Returns (dQ bf16 [s_q,h_q,576], dKV fp32 shaped like kv).
+
+    Positional arguments and defaults are the reference operator's: base-2 `lse`, sm_scale =
+    1/sqrt(576), and the causal rule "slot valid only if idx <= query row" (`q_start_index_s=0`,
+    `mla_bwd/mla_bwd.cu:122,772`).  Pass `q_start_index_s=None` to keep only the range check.
+    `out_dkv` + `accumulate=True` add into an existing fp32 buffer (partial dKV of a query shard).
+    The call enqueues on the current stream and does not synchronise unless
+    `check_device_status=True`, which also raises if a kernel reported a timed-out wait.
+    """
+    _validate(q, kv, dO, lse, O, indices)
+    lib = load_library()
+    kv2 = kv.reshape(kv.shape[0], D_QK)
+    idx2 = indices.reshape(indices.shape[0], indices.shape[-1])
+    with torch.cuda.device(q.device):
+        dQ = torch.empty_like(q)
+        if out_dkv is None:
+            dKV = torch.empty(kv.shape, dtype=torch.float32, device=q.device)
+            _check(not accumulate, "accumulate=True needs out_dkv")
+        else:
+            _check(out_dkv.is_cuda and out_dkv.dtype == torch.float32 and out_dkv.is_contiguous()
+                   and out_dkv.numel() == kv.numel(), "out_dkv must be a contiguous fp32 CUDA tensor shaped like kv")
+            dKV = out_dkv
+        params = _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV, sm_scale, q_start_index_s, lse_is_base2)
+        if workspace is None:
+            need = lib.smla_bwd_workspace_size(ctypes.byref(params), workspace_budget)
+            _check(need > 0, "unsupported shapes for the sparse MLA backward")
+            workspace = Workspace(need, q.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        stages = STAGE_ALL & ~STAGE_ZERO if accumulate else STAGE_ALL
+        st = lib.smla_bwd_run_stages(ctypes.byref(params), workspace.ptr, workspace.nbytes, stream, stages)
+        _raise_status(lib, st, "smla_bwd_run")
+        if check_device_status:
+            _raise_status(lib, lib.smla_bwd_status(workspace.ptr, stream), "smla_bwd device status")
+    return dQ, dKV
+
+
+def run_stages(q, kv, dO, lse, O, indices, dQ, dKV, workspace: Workspace, stages: int, sm_scale=None,
+               q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True) -> WorkspaceLayout:
+    """Run selected kernels (bit mask of STAGE_*) on caller-owned outputs; returns the workspace layout.
+    For stage-by-stage tests and for profiling one kernel at a time."""
+    _validate(q, kv, dO, lse, O, indices)
+    lib = load_library()
+    kv2 = kv.reshape(kv.shape[0], D_QK)
+    idx2 = indices.reshape(indices.shape[0], indices.shape[-1])
+    params = _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV, sm_scale, q_start_index_s, lse_is_base2)
+    lay = WorkspaceLayout()
+    with torch.cuda.device(q.device):
+        _raise_status(lib, lib.smla_bwd_get_workspace_layout(ctypes.byref(params), workspace.nbytes, ctypes.byref(lay)),
+                      "smla_bwd_get_workspace_layout")
+        stream = torch.cuda.current_stream().cuda_stream
+        _raise_status(lib, lib.smla_bwd_run_stages(ctypes.byref(params), workspace.ptr, workspace.nbytes, stream, stages),
+                      "smla_bwd_run_stages")
+    return lay
+
+
+def workspace_for(q, kv, indices, budget: int = 0) -> Workspace:
+    """Allocate a workspace big enough for these shapes (at most about `budget` bytes when non-zero)."""
+    lib = load_library()
+    p = _Params(0, 0, 0, 0, 0, 0, 0, 0, q.shape[0], kv.shape[0], q.shape[1], indices.shape[-1], 0.0, 0, 1)
+    need = lib.smla_bwd_workspace_size(ctypes.byref(p), budget)
+    _check(need > 0, "unsupported shapes for the sparse MLA backward")
+    return Workspace(need, q.device)
+
+
+def device_status(workspace: Workspace) -> int:
+    """Synchronise the current stream and return the library status word (0 = ok)."""
+    lib = load_library()
+    return lib.smla_bwd_status(workspace.ptr, torch.cuda.current_stream().cuda_stream)
+
+
+def delta(O: torch.Tensor, dO: torch.Tensor) -> torch.Tensor:
+    """Delta = rowsum(O * dO), fp32 [s_q, h_q] (reference: `launch_preprocess_delta`, `mla_bwd/mla_bwd.cu:802-819`)."""
+    _check(O.is_cuda and dO.is_cuda and O.dtype == torch.bfloat16 and dO.dtype == torch.bfloat16, "O, dO: CUDA bf16")
+    _check(O.is_contiguous() and dO.is_contiguous() and O.shape == dO.shape and O.shape[-1] == D_V, "O, dO shape")
+    lib = load_library()
+    out = torch.empty(O.shape[:-1], dtype=torch.float32, device=O.device)
+    with torch.cuda.device(O.device):
+        st = lib.smla_bwd_delta(O.data_ptr(), dO.data_ptr(), out.data_ptr(), O.shape[0], O.shape[1],
+                                torch.cuda.current_stream().cuda_stream)
+    _raise_status(lib, st, "smla_bwd_delta")
+    return out
+
+
+def last_launch_count() -> int:
+    return load_library().smla_bwd_last_launch_count()
