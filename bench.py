@@ -1,0 +1,356 @@
+#!/usr/bin/env python3
+"""Benchmark of the sparse MLA attention backward (5504 FLOPs per query x head x top-k slot).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--s-q ROWS] [--stages MASK]
+
+One JSON line on stdout (rank 0).  A step is one backward over the whole workload:
+  N = 1   workload "head128"  (s_q 4096, s_kv 32768, h_q 128, top-k 2048), one sequence
+  N > 1   workload "batch_sharded" (8 independent sequences of s_q 8192, s_kv 16384, h_q 128, top-k 2048)
+          split round-robin over the ranks, no communication -> strong scaling;
+          `--workload query_sharded` runs the long sequence split by queries + NCCL reduce-scatter of dKV.
+`value` times the operator with inputs resident in HBM; `e2e` times it from pinned host buffers
+(copies in and results out inside the timed region).  `--impl reference` times the reference's
+CPU algorithm (the oracle port) on the host cores.  `--s-q` / `--stages` cut the workload down
+for profiler captures and are reported in `config`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from test_operator_b200.inputs import WORKLOADS, make_sequence  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+STAGE_NAMES = {2: "delta", 4: "recompute", 8: "dkv", 16: "dq"}
+# share of the 5504 FLOPs per slot each kernel carries: recompute = P + dP, dkv = dV + dK, dq = dQ
+STAGE_FLOP_SHARE = {4: (2 * 576 + 2 * 512) / 5504.0, 8: (2 * 512 + 2 * 576) / 5504.0, 16: 2 * 576 / 5504.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def _dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def _oracle_tflops(seq, w, n_queries: int, threads: int):
+    """Time the CPU oracle on the first n_queries rows of `seq` (all top-k slots, full kv)."""
+    from oracle.sparse_mla_ref import sparse_mla_bwd_ref
+    torch.set_num_threads(threads)
+    cpu = {k: (v[:n_queries].cpu() if k in ("q", "dO", "lse", "O", "indices") else
+               (v.cpu() if torch.is_tensor(v) else v)) for k, v in seq.items()}
+    t0 = time.perf_counter()
+    sparse_mla_bwd_ref(cpu["q"], cpu["kv"], cpu["dO"], cpu["lse"], cpu["O"], cpu["indices"],
+                       q_start_index_s=cpu["q_start_index_s"])
+    dt = time.perf_counter() - t0
+    return 5504.0 * n_queries * w.h_q * w.topk / dt / 1e12, dt
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path, all host threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wname = args.workload or ("head128" if args.gpus == 1 else "batch_sharded")
+    w = WORKLOADS[wname]
+    threads = os.cpu_count() or 1
+    n_step = args.s_q or 32
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    seq = make_sequence(w, 0, device=dev, s_q_override=n_step)
+    seq = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in seq.items()}
+    times = []
+    for i in range(args.warmup + args.steps):
+        _, dt = _oracle_tflops(seq, w, n_step, threads)
+        if i >= args.warmup:
+            times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    val = 5504.0 * n_step * w.h_q * w.topk / (ms * 1e-3) / 1e12
+    sample = f"{n_step} of {w.s_q} queries of sequence 0 per step, full kv and top-k"
+    print(json.dumps({
+        "impl": "reference", "metric": "sparse_mla_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wname, "s_q": w.s_q, "s_kv": w.s_kv, "h_q": w.h_q, "topk": w.topk,
+                   "batch": w.batch, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def run_ours(args):
+    from test_operator_b200 import op, sharding
+    import torch.distributed as dist
+
+    rank, world, local = _dist_setup(args.gpus)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sparse MLA backward has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    wname = args.workload or ("head128" if world == 1 else "batch_sharded")
+    w = WORKLOADS[wname]
+    query_sharded = wname == "query_sharded" and world > 1
+    stages = args.stages or op.STAGE_ALL
+
+    # ---- this rank's share of the workload, resident in HBM -------------------------------------------
+    if query_sharded:
+        full = make_sequence(w, 0, device=dev, s_q_override=args.s_q)
+        r0, r1 = sharding.query_block(full["q"].shape[0], rank, world)
+        seqs = [{k: (v[r0:r1].contiguous() if k in ("q", "dO", "lse", "O", "indices") else v) for k, v in full.items()}]
+        seqs[0]["row0"] = r0
+        del full
+        my_queries = r1 - r0
+    else:
+        ids = sharding.sequences_of_rank(w.batch, rank, world)
+        seqs = [make_sequence(w, b, device=dev, s_q_override=args.s_q) for b in ids]
+        my_queries = sum(s["q"].shape[0] for s in seqs)
+    total_q = torch.tensor([my_queries], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_q)
+    flops = 5504.0 * int(total_q.item()) * w.h_q * w.topk
+    ws = op.workspace_for(seqs[0]["q"], seqs[0]["kv"], seqs[0]["indices"]) if seqs else None
+    partial = torch.empty(seqs[0]["kv"].shape, dtype=torch.float32, device=dev) if query_sharded else None
+
+    launches = [0]
+
+    def step():
+        outs = []
+        for s in seqs:
+            if query_sharded:
+                outs.append(sharding.query_sharded_bwd(op.mla_bwd, s["q"], s["kv"], s["dO"], s["lse"], s["O"],
+                                                       s["indices"], s["row0"], s["q_start_index_s"],
+                                                       partial=partial, workspace=ws))
+            elif stages == op.STAGE_ALL:
+                outs.append(op.mla_bwd(s["q"], s["kv"], s["dO"], s["lse"], s["O"], s["indices"],
+                                       q_start_index_s=s["q_start_index_s"], workspace=ws))
+            else:
+                dq = torch.empty_like(s["q"])
+                dkv = torch.empty(s["kv"].shape, dtype=torch.float32, device=dev)
+                op.run_stages(s["q"], s["kv"], s["dO"], s["lse"], s["O"], s["indices"], dq, dkv, ws, stages,
+                              q_start_index_s=s["q_start_index_s"])
+            launches[0] += op.last_launch_count()
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches[0] = 0
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    n_launch = launches[0]
+    if ws is not None and op.device_status(ws) != 0:
+        raise SystemExit("device reported a timed-out wait: results invalid")
+
+    # ---- per-kernel times (rank 0's first sequence), for the roofline of the dominant kernel -------------
+    kernels = {}
+    if seqs and not query_sharded:
+        s = seqs[0]
+        dq = torch.empty_like(s["q"])
+        dkv = torch.zeros(s["kv"].shape, dtype=torch.float32, device=dev)
+        nq = s["q"].shape[0]
+        for bit, name in STAGE_NAMES.items():
+            if not (stages & bit):
+                continue
+            ts = []
+            for i in range(4):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                op.run_stages(s["q"], s["kv"], s["dO"], s["lse"], s["O"], s["indices"], dq, dkv, ws, bit,
+                              q_start_index_s=s["q_start_index_s"])
+                b.record()
+                torch.cuda.synchronize()
+                if i:
+                    ts.append(a.elapsed_time(b))
+            kms = sum(ts) / len(ts)
+            entry = {"ms": kms}
+            if bit in STAGE_FLOP_SHARE:
+                entry["tflops"] = STAGE_FLOP_SHARE[bit] * 5504.0 * nq * w.h_q * w.topk / (kms * 1e-3) / 1e12
+            else:
+                entry["gbs"] = 2.0 * nq * w.h_q * 512 * 2 / (kms * 1e-3) / 1e9
+            kernels[name] = entry
+    peaks, peak_kind = load_peaks()
+    roofline = None
+    mm = {k: v for k, v in kernels.items() if "tflops" in v}
+    if mm:
+        dom = max(mm, key=lambda k: mm[k]["ms"])
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))  # burst: kernel timed alone
+        roofline = {"bound": "tensor", "kernel": f"smla_{dom}_kernel", "achieved": mm[dom]["tflops"], "peak": peak,
+                    "unit": "TFLOP/s", "frac": mm[dom]["tflops"] / peak, "peak_kind": peak_kind + " burst",
+                    "traffic": None}
+
+    # ---- end to end from pinned host buffers --------------------------------------------------------------
+    e2e = None
+    if seqs and not query_sharded and stages == op.STAGE_ALL and not args.no_e2e:
+        host = []
+        h2d = d2h = 0
+        for s in seqs:
+            hs = {k: (v.cpu().pin_memory() if torch.is_tensor(v) else v) for k, v in s.items()}
+            host.append(hs)
+            h2d += sum(v.numel() * v.element_size() for v in hs.values() if torch.is_tensor(v))
+            d2h += s["q"].numel() * 2 + s["kv"].numel() * 4
+        out_pinned = [(torch.empty(s["q"].shape, dtype=torch.bfloat16).pin_memory(),
+                       torch.empty(s["kv"].shape, dtype=torch.float32).pin_memory()) for s in seqs]
+        n_e2e = max(1, min(args.steps, 3))
+
+        def e2e_step():
+            for hs, (hq, hkv) in zip(host, out_pinned):
+                op.mla_bwd_host(hs["q"], hs["kv"], hs["dO"], hs["lse"], hs["O"], hs["indices"], device=dev,
+                                q_start_index_s=hs["q_start_index_s"], workspace=ws, out_dq=hq, out_dkv=hkv)
+
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            e2e_step()
+        barrier()
+        e_ms = 1e3 * (time.perf_counter() - t0) / n_e2e
+        te = torch.tensor([e_ms], dtype=torch.float64, device=dev)
+        hb = torch.tensor([h2d, d2h], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            dist.all_reduce(hb)
+        e2e = {"value": flops / (float(te.item()) * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": float(te.item()),
+               "h2d_bytes_per_step": int(hb[0].item()), "d2h_bytes_per_step": int(hb[1].item()), "steps": n_e2e}
+
+    # ---- CPU baseline (rank 0, one GPU only): the oracle port on a bounded sample ------------------------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and seqs and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        _, dt = _oracle_tflops(seqs[0], w, 8, threads)          # calibrate
+        n = int(max(16, min(seqs[0]["q"].shape[0], 15.0 / max(dt / 8, 1e-4))))
+        n = min(n, 2048)
+        val, dt = _oracle_tflops(seqs[0], w, n, threads)
+        cpu_baseline = {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"first {n} of {seqs[0]['q'].shape[0]} queries of sequence 0, full kv and top-k, {dt:.1f} s"}
+
+    if rank == 0:
+        out = {
+            "metric": "sparse_mla_bwd_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wname, "batch": w.batch, "s_q": args.s_q or w.s_q, "s_kv": w.s_kv, "h_q": w.h_q,
+                       "topk": w.topk, "d_qk": 576, "d_v": 512, "flops_per_slot": 5504,
+                       "sharding": ("query+reduce_scatter" if query_sharded else "batch") if world > 1 else "none",
+                       "stages": stages, "l2": "inputs larger than L2 (no flush)"},
+            "clocks": clocks, "gpu_launches": n_launch, "kernels": kernels,
+        }
+        if roofline:
+            out["roofline"] = roofline
+        if e2e:
+            out["e2e"] = e2e
+        if cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--s-q", dest="s_q", type=int, default=None, help="keep only the first rows of the query dimension")
+    ap.add_argument("--stages", type=int, default=0, help="bit mask of kernels to run (profiling); 0 = all")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

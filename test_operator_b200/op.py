@@ -246,3 +246,25 @@ def delta(O: torch.Tensor, dO: torch.Tensor) -> torch.Tensor:
 
 def last_launch_count() -> int:
     return load_library().smla_bwd_last_launch_count()
+
+
+def mla_bwd_host(q, kv, dO, lse, O, indices, device, sm_scale: Optional[float] = None,
+                 q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True,
+                 workspace: Optional[Workspace] = None, out_dq: Optional[torch.Tensor] = None,
+                 out_dkv: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same operator for HOST tensors: copies the inputs to `device`, runs the backward there and
+    returns (dQ, dKV) as host tensors (written into `out_dq` / `out_dkv` when given; pinned buffers
+    make the copies asynchronous).  Synchronises before returning."""
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        d = [t.to(dev, non_blocking=True) for t in (q, kv, dO, lse, O, indices)]
+        dq, dkv = mla_bwd(*d, sm_scale=sm_scale, q_start_index_s=q_start_index_s, lse_is_base2=lse_is_base2,
+                          workspace=workspace)
+        if out_dq is None:
+            out_dq = torch.empty(dq.shape, dtype=dq.dtype, pin_memory=True)
+        if out_dkv is None:
+            out_dkv = torch.empty(dkv.shape, dtype=dkv.dtype, pin_memory=True)
+        out_dq.copy_(dq, non_blocking=True)
+        out_dkv.copy_(dkv, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    return out_dq, out_dkv
