@@ -121,7 +121,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     __nv_bfloat16* ds_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.ds_off);
     float* delta = reinterpret_cast<float*>(ws + pl.delta_off);
 
-    CUtensorMap tm_q64, tm_do64, tm_qhp, tm_dohp, tm_kv, tm_s, tm_ds;
+    CUtensorMap tm_q64, tm_do64, tm_qhp, tm_dohp, tm_s, tm_ds;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
     const uint64_t srows = uint64_t(pl.q_chunk) * pl.topk_pad;
     bool ok = true;
@@ -129,7 +129,6 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     ok &= make_map_2d(&tm_do64, p->dO, kDV, qrows, kDV * 2, 64, 64);
     ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
     ok &= make_map_2d(&tm_dohp, p->dO, kDV, qrows, kDV * 2, 64, HP);
-    ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
     ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
     ok &= make_map_2d(&tm_ds, ds_scr, HP, srows, HP * 2, 64, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
@@ -141,6 +140,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
     KParams kp{};
+    kp.kv = reinterpret_cast<const __nv_bfloat16*>(p->kv);
     kp.indices = p->indices;
     kp.lse = p->lse;
     kp.delta = delta;
@@ -170,7 +170,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         if (stages & SMLA_STAGE_RECOMPUTE) {
-            smla_recompute_kernel<HP><<<nq * (HP / 64), rc::kThreads, rc::kSmemBytes, st>>>(tm_q64, tm_do64, tm_kv, kp);
+            smla_recompute_kernel<HP><<<nq * (HP / 64), rc::kThreads, rc::kSmemBytes, st>>>(tm_q64, tm_do64, kp);
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DKV) {
@@ -178,7 +178,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DQ) {
-            smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_ds, kp);
+            smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_ds, kp);
             ++g_last_launches;
         }
     }

@@ -30,6 +30,7 @@ constexpr int kVChunks = kDV / 64;    // 8
 constexpr int kSplitChunk = 5;        // d-part 0 = chunks [0,5) = columns [0,320); part 1 = chunks [5,9)
 
 struct KParams {
+    const __nv_bfloat16* kv;  // [s_kv, 576]
     const int32_t* indices;   // [s_q, topk]
     const float* lse;         // [s_q, h_q]
     const float* delta;       // [s_q, h_q]
@@ -83,18 +84,22 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 }
 
 // =============================================================================================
-// recompute: one CTA per (query, group of 64 heads).
-//   warp 0      producer: Q / dO chunks of its head group once (TMA tiled), then per 128-key tile
-//               nine [128 keys x 64 col] chunks of gathered kv rows (TMA gather4, 4 rows per lane)
-//   warp 1      UMMA issuer: P^T[128 keys, 64 heads] += Kg_chunk . Q_chunk^T  (9 chunks, K = 576)
-//                            dP^T                    += Kg_chunk . dO_chunk^T (8 chunks, K = 512)
-//               accumulators double-buffered in TMEM (2 x 128 columns)
-//   warps 2-5   softmax-gradient: thread = key row; reads P^T, dP^T from TMEM, writes one 128-byte
+// recompute: one CTA per (query, group of 64 heads), 13 warps.
+//   warps 0-3   softmax-gradient: thread = key row; reads P^T, dP^T from TMEM, writes one 128-byte
 //               row of S and of dS (bf16) to the scratch
+//   warps 4-11  gather producers: per 128-key tile nine [128 keys x 64 col] chunks of kv rows picked by
+//               index, copied with 16-byte cp.async into the 128-byte-swizzled layout the UMMA reads
+//               (the TMA gather4 path tops out near 8 B/clk per SM; 256 threads of cp.async reach ~20)
+//   warp 12     UMMA issuer (+ TMEM allocation, + the Q / dO chunks of the head group by TMA):
+//               P^T[128 keys, 64 heads] += Kg_chunk . Q_chunk^T  (9 chunks, K = 576)
+//               dP^T                    += Kg_chunk . dO_chunk^T (8 chunks, K = 512)
+//               accumulators double-buffered in TMEM (2 x 128 columns)
 // =============================================================================================
 namespace rc {
-constexpr int kThreads = 192;
+constexpr int kThreads = 416;
+constexpr int kProducerWarps = 8;
 constexpr int kStages = 5;
+constexpr int kLag = 3;                        // cp.async groups a producer thread keeps in flight
 constexpr int kTileKeys = 128;
 constexpr int kChunkBytesA = kTileKeys * 128;  // 16 KB gathered chunk
 constexpr int kChunkBytesB = 64 * 128;         // 8 KB Q / dO chunk (64 heads)
@@ -108,7 +113,7 @@ constexpr int kSmemBytes = kOffMisc + 1024 + 1024;  // + misc + alignment slack
 template <int HP>
 __global__ void __launch_bounds__(rc::kThreads, 1)
 smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                      const __grid_constant__ CUtensorMap tm_kv, const KParams p) {
+                      const KParams p) {
     using namespace rc;
     constexpr int G = HP / 64;
     const int g = blockIdx.x % G;
@@ -137,7 +142,7 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (threadIdx.x == 0) {
         *s_abort = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_full + 8 * i, kProducerWarps);
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_qdo, 1);
@@ -147,7 +152,7 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == 12) {
         tmem_alloc(smem_u32(tmem_slot), 256);
         tmem_relinquish();
     }
@@ -157,39 +162,53 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer
+    if (warp >= 4 && warp < 12) {
+        // ------------------------------------------------------------------ gather producers
+        const int pt = threadIdx.x - 128;   // 0..255
+        const int u = pt & 7;               // 16-byte unit inside a 128-byte chunk row
+        const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of the tile
+        const uint32_t dst0 = s_base + kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
+        const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
+        int it = 0;
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const char* src[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = tile * kTileKeys + r0 + 32 * i;
+                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                idx = min(max(idx, 0), p.s_kv - 1);   // unused slots gather a real row; their S, dS are forced to 0
+                src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
+            }
+            for (int j = 0; j < kQChunks; ++j, ++it) {
+                const int s = it % kStages;
+                mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 1);
+                const uint32_t d = dst0 + s * kChunkBytesA;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) cp_async16(d + i * 32 * 128, src[i] + j * 128);
+                cp_async_commit();
+                if (it >= kLag) {
+                    cp_async_wait<kLag>();
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
+                }
+            }
+        }
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0)
+            for (int d = (it < kLag ? it : kLag); d >= 1; --d) mbar_arrive(bar_full + 8 * ((it - d) % kStages));
+    } else if (warp == 12) {
+        // ------------------------------------------------------------------ UMMA issuer
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_do);
-            tma_prefetch_desc(&tm_kv);
             mbar_arrive_expect_tx(bar_qdo, (kQChunks + kVChunks) * kChunkBytesB);
             const int row0 = qg * p.h_q + 64 * g;
             for (int j = 0; j < kQChunks; ++j) tma_load_2d(s_base + kOffQ + j * kChunkBytesB, &tm_q, 64 * j, row0, bar_qdo);
             for (int j = 0; j < kVChunks; ++j) tma_load_2d(s_base + kOffDO + j * kChunkBytesB, &tm_do, 64 * j, row0, bar_qdo);
-        }
-        int it = 0;
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            int r[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int key = tile * kTileKeys + lane * 4 + k;
-                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                r[k] = min(max(idx, 0), p.s_kv - 1);  // unused slots gather a real row; their S, dS are forced to 0
-            }
-            for (int j = 0; j < kQChunks; ++j, ++it) {
-                const int s = it % kStages;
-                const uint32_t ph = (it / kStages) & 1;
-                mbar_wait(bar_empty + 8 * s, ph ^ 1, wc, kErrRecompute + 1);
-                if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, kChunkBytesA);
-                __syncwarp();
-                tma_gather4(s_base + kOffRing + s * kChunkBytesA + lane * 512, &tm_kv, 64 * j, r[0], r[1], r[2], r[3],
-                            bar_full + 8 * s);
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+
             constexpr uint32_t idesc = make_idesc_bf16(128, 64, 0, 0);
             mbar_wait(bar_qdo, 0, wc, kErrRecompute + 2);
             int it = 0;
@@ -220,8 +239,8 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
     } else {
         // ------------------------------------------------------------------ softmax gradient
-        const int quarter = warp & 3;
-        const int st = threadIdx.x - 64;  // 0..127
+        const int quarter = warp;
+        const int st = threadIdx.x;  // 0..127
         if (st < 64) {
             const int h = 64 * g + st;
             const bool hv = h < p.h_q;
@@ -241,7 +260,7 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + 64 * g;
             uint4* s_out = reinterpret_cast<uint4*>(p.s_scr + off);
             uint4* ds_out = reinterpret_cast<uint4*>(p.ds_scr + off);
-#pragma unroll
+#pragma unroll 1
             for (int half = 0; half < 2; ++half) {
                 uint32_t pv[32], dpv[32];
                 tmem_ld_32x32(taddr + half * 32, pv);
@@ -254,9 +273,9 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int h = half * 32 + c + e;
-                        const float s = valid ? ex2_approx(fmaf(__uint_as_float(pv[c + e]), p.scale_log2e, -lse_s[h])) : 0.f;
-                        sv[e] = s;
-                        dsv[e] = valid ? s * (__uint_as_float(dpv[c + e]) - delta_s[h]) * p.sm_scale : 0.f;
+                        const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c + e]), p.scale_log2e, -lse_s[h])) : 0.f;
+                        sv[e] = sx;
+                        dsv[e] = valid ? sx * (__uint_as_float(dpv[c + e]) - delta_s[h]) * p.sm_scale : 0.f;
                     }
                     so[c >> 1] = pack_bf16x2(sv[0], sv[1]);
                     dso[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
@@ -274,7 +293,7 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 256);
+    if (warp == 12) tmem_dealloc(tmem, 256);
 }
 
 // =============================================================================================
@@ -284,12 +303,13 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 //   warp 0     producer: resident chunks once, then per 64-key tile the S and dS scratch tiles
 //              [64 keys x HP heads] (B operand, K-major)
 //   warp 1     UMMA issuer: acc[blk][128 d, 64 keys] = dO^T . S + Q^T . dS, double-buffered in TMEM
-//   warps 2-5  drain: thread = d row; one fp32 reduction per key, 32 lanes -> 128 contiguous bytes
+//   warps 2-9  drain: thread = d row, each warp owns 32 d rows x 32 keys of a tile; one fp32 reduction
+//              per key, 32 lanes -> 128 contiguous bytes
 // Part 0's third block has 64 real rows (d 256..319); its upper 64 rows read whatever follows
 // in shared memory and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
 // =============================================================================================
 namespace dk {
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // warp 0 producer, warp 1 UMMA issuer, warps 2-9 drain
 constexpr int kTileKeys = 64;
 constexpr int kResChunks = 5;
 template <int HP> struct Cfg {
@@ -300,7 +320,8 @@ template <int HP> struct Cfg {
     static constexpr int kOffDO = kResChunks * kChunk;
     static constexpr int kOffStage = 2 * kResChunks * kChunk;
     static constexpr int kOffMisc = kOffStage + 2 * kStage;
-    static constexpr int kSmemBytes = kOffMisc + 256 + 1024;
+    static constexpr int kOffIdx = kOffMisc + 128;          // 8 drain warps x 32 int
+    static constexpr int kSmemBytes = kOffMisc + 128 + 1024 + 1024;
     static constexpr int kAccCols = 192;                    // 3 blocks x 64 keys per buffer
 };
 }  // namespace dk
@@ -340,7 +361,7 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 1);
             mbar_init(bar_afull + 8 * i, 1);
-            mbar_init(bar_aempty + 8 * i, 4);
+            mbar_init(bar_aempty + 8 * i, 8);
         }
         mbar_init(bar_res, 1);
         fence_mbar_init();
@@ -417,33 +438,37 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     } else {
         const int quarter = warp & 3;
+        const int e = (warp - 2) >> 2;          // which 32 keys of the 64-key tile this warp scatters
         const int d_part0 = chunk0 * 64;
+        int* idx_s = reinterpret_cast<int*>(smem + C::kOffIdx) + (warp - 2) * 32;
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile & 1;
-            int idx2[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
+            {
                 const int key = tile * kTileKeys + 32 * e + lane;
                 const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                idx2[e] = slot_valid(idx, qg, p) ? idx : -1;
+                __syncwarp();
+                idx_s[lane] = slot_valid(idx, qg, p) ? idx : -1;
+                __syncwarp();
+            }
+            int ix[32];
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                const int4 t = reinterpret_cast<const int4*>(idx_s)[v];
+                ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
             }
             mbar_wait(bar_afull + 8 * s, (tile >> 1) & 1, wc, kErrDkv + 5);
             tc_fence_after_sync();
             for (int blk = 0; blk < n_blk; ++blk) {
                 if (part == 0 && blk == 2 && quarter >= 2) continue;  // padded rows
                 float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane;
-                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + s * C::kAccCols + blk * 64;
+                const uint32_t taddr =
+                    tmem + (static_cast<uint32_t>(quarter * 32) << 16) + s * C::kAccCols + blk * 64 + 32 * e;
+                uint32_t r[32];
+                tmem_ld_32x32(taddr, r);
+                tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + 32 * e, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int idx = __shfl_sync(0xffffffffu, idx2[e], j);
-                        if (idx >= 0) red_add_f32(out + static_cast<size_t>(idx) * kDQK, __uint_as_float(r[j]));
-                    }
-                }
+                for (int j = 0; j < 32; ++j)
+                    if (ix[j] >= 0) red_add_f32(out + static_cast<size_t>(ix[j]) * kDQK, __uint_as_float(r[j]));
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -456,17 +481,19 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // =============================================================================================
-// dq: one CTA per (query, d-part); same d split as dkv.
-//   warp 0     producer: per 64-key tile the dS scratch tile [64 keys x HP heads] (TMA tiled) and
-//              the part's columns of the gathered kv rows (TMA gather4, lanes 0-15 x 4 rows)
-//   warp 1     UMMA issuer: acc[blk][128 d, HP heads] += Kg^T . dS^T  (both operands MN-major:
-//              the key index is the contraction and runs along shared-memory rows)
-//   warps 2-5  epilogue: TMEM -> bf16 -> dQ[q, head, d]
+// dq: one CTA per (query, d-part); same d split as dkv; 13 warps.
+//   warps 0-3   epilogue: TMEM -> bf16 -> dQ[q, head, d]
+//   warps 4-11  producers: per 64-key tile the part's columns of the kv rows picked by index (16-byte
+//               cp.async into the swizzled layout); thread 128 also issues the TMA load of the dS tile
+//   warp 12     UMMA issuer: acc[blk][128 d, HP heads] += Kg^T . dS^T  (both operands MN-major:
+//               the key index is the contraction and runs along shared-memory rows)
 // =============================================================================================
 namespace dq {
-constexpr int kThreads = 192;
+constexpr int kThreads = 416;
+constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
 constexpr int kStages = 3;
+constexpr int kLag = 2;
 template <int HP> struct Cfg {
     static constexpr int kKgBytes = 5 * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
@@ -479,7 +506,7 @@ template <int HP> struct Cfg {
 
 template <int HP>
 __global__ void __launch_bounds__(dq::kThreads, 1)
-smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
+smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
     using C = Cfg<HP>;
     const int part = blockIdx.x & 1;
@@ -505,13 +532,13 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     if (threadIdx.x == 0) {
         *s_abort = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_full + 8 * i, kProducerWarps + 1);   // 8 producer warps + the TMA expect_tx arrival
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_acc, 1);
         fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == 12) {
         tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
         tmem_relinquish();
     }
@@ -521,37 +548,49 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
 
-    if (warp == 0) {
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_kv);
-            tma_prefetch_desc(&tm_ds);
-        }
+    if (warp >= 4 && warp < 12) {
+        const int pt = threadIdx.x - 128;   // 0..255
+        const int u = pt & 7;
+        const int r0 = pt >> 3;             // rows r0 and r0+32 of the tile
+        const uint32_t dst0 = s_base + r0 * 128 + ((u ^ (r0 & 7)) << 4);
+        const char* kvb = reinterpret_cast<const char*>(p.kv) + chunk0 * 128 + u * 16;
+        if (pt == 0) tma_prefetch_desc(&tm_ds);
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile % kStages;
-            int r[4] = {0, 0, 0, 0};
-            if (lane < 16) {
+            const char* src[2];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int key = tile * kTileKeys + lane * 4 + k;
-                    int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                    r[k] = min(max(idx, 0), p.s_kv - 1);
-                }
+            for (int i = 0; i < 2; ++i) {
+                const int key = tile * kTileKeys + r0 + 32 * i;
+                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                idx = min(max(idx, 0), p.s_kv - 1);
+                src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1);
-            const uint32_t dst = s_base + s * C::kStage;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(bar_full + 8 * s, n_ch * 8192 + C::kDsBytes);
+            const uint32_t d = dst0 + s * C::kStage;
+            if (pt == 0) {
+                mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes);
                 const int row = ql * p.topk_pad + tile * kTileKeys;
-                for (int c = 0; c < HP / 64; ++c) tma_load_2d(dst + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
+                for (int c = 0; c < HP / 64; ++c)
+                    tma_load_2d(s_base + s * C::kStage + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
             }
-            __syncwarp();
-            if (lane < 16) {
-                for (int c = 0; c < n_ch; ++c)
-                    tma_gather4(dst + c * 8192 + lane * 512, &tm_kv, 64 * (chunk0 + c), r[0], r[1], r[2], r[3],
-                                bar_full + 8 * s);
+            for (int c = 0; c < n_ch; ++c) {
+                cp_async16(d + c * 8192, src[0] + c * 128);
+                cp_async16(d + c * 8192 + 32 * 128, src[1] + c * 128);
+            }
+            cp_async_commit();
+            if (tile >= kLag) {
+                cp_async_wait<kLag>();
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * ((tile - kLag) % kStages));
             }
         }
-    } else if (warp == 1) {
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0)
+            for (int d = (n_tiles < kLag ? n_tiles : kLag); d >= 1; --d) mbar_arrive(bar_full + 8 * ((n_tiles - d) % kStages));
+    } else if (warp == 12) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_bf16(128, HP, 1, 1);
             for (int tile = 0; tile < n_tiles; ++tile) {
@@ -571,7 +610,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
             umma_commit(bar_acc);
         }
     } else {
-        const int quarter = warp & 3;
+        const int quarter = warp;
         mbar_wait(bar_acc, 0, wc, kErrDq + 3);
         tc_fence_after_sync();
         for (int blk = 0; blk < n_blk; ++blk) {
@@ -594,7 +633,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, C::kTmemCols);
+    if (warp == 12) tmem_dealloc(tmem, C::kTmemCols);
 }
 
 }  // namespace smla
