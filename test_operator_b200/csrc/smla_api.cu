@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/smla_bwd.h"
@@ -58,7 +59,7 @@ bool make_map_2d(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows,
 
 struct Plan {
     int h_pad;       // heads padded to 64 or 128
-    int topk_pad;    // top-k padded to a multiple of 128
+    int topk_pad;    // top-k padded to a multiple of 256
     int q_chunk;     // queries per pass
     size_t err_off, delta_off, s_off, ds_off, total;
 };
@@ -75,7 +76,7 @@ bool check_params(const smla_bwd_params* p) {
 bool make_plan(const smla_bwd_params* p, size_t budget, Plan* pl) {
     if (!check_params(p)) return false;
     pl->h_pad = p->h_q <= 64 ? 64 : 128;
-    pl->topk_pad = (p->topk + 127) / 128 * 128;
+    pl->topk_pad = (p->topk + 255) / 256 * 256;   // the pair recompute kernel walks 256-key tiles
     const size_t per_q = size_t(pl->topk_pad) * pl->h_pad * 2 /*bf16*/ * 2 /*S and dS*/;
     pl->err_off = 0;
     pl->delta_off = kAlign;
@@ -121,20 +122,21 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     __nv_bfloat16* ds_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.ds_off);
     float* delta = reinterpret_cast<float*>(ws + pl.delta_off);
 
-    CUtensorMap tm_q64, tm_do64, tm_qhp, tm_dohp, tm_s, tm_ds;
+    CUtensorMap tm_qnh, tm_donh, tm_qhp, tm_dohp, tm_kv, tm_s, tm_ds;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
     const uint64_t srows = uint64_t(pl.q_chunk) * pl.topk_pad;
     bool ok = true;
-    ok &= make_map_2d(&tm_q64, p->q, kDQK, qrows, kDQK * 2, 64, 64);
-    ok &= make_map_2d(&tm_do64, p->dO, kDV, qrows, kDV * 2, 64, 64);
+    ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
+    ok &= make_map_2d(&tm_donh, p->dO, kDV, qrows, kDV * 2, 64, HP / 2);
     ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
     ok &= make_map_2d(&tm_dohp, p->dO, kDV, qrows, kDV * 2, 64, HP);
+    ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
     ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
     ok &= make_map_2d(&tm_ds, ds_scr, HP, srows, HP * 2, 64, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
 
     // per device, so set on every call (cheap) rather than once per process
-    bool attr_ok = set_smem(smla_recompute_kernel<HP>, rc::kSmemBytes);
+    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP>, rp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_kernel<HP>, dk::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dq_kernel<HP>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
@@ -159,6 +161,10 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     kp.lse_mult = p->lse_is_base2 ? 1.0f : 1.4426950408889634f;
     kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
     kp.q_start = kp.causal ? p->q_start_index_s : 0;
+#ifdef SMLA_DEBUG_KNOBS
+    kp.dbg = getenv("SMLA_DBG") ? atoi(getenv("SMLA_DBG")) : 0;
+    kp.dbg_buf = reinterpret_cast<long long*>(ws + 128);   // spare bytes behind the error word
+#endif
 
     if (stages & SMLA_STAGE_DELTA) {
         const int n_rows = p->s_q * p->h_q;
@@ -170,7 +176,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         if (stages & SMLA_STAGE_RECOMPUTE) {
-            smla_recompute_kernel<HP><<<nq * (HP / 64), rc::kThreads, rc::kSmemBytes, st>>>(tm_q64, tm_do64, kp);
+            smla_recompute_pair_kernel<HP><<<nq * 2, rp::kThreads, rp::Cfg<HP>::kSmemBytes, st>>>(tm_qnh, tm_donh, kp);
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DKV) {
@@ -178,7 +184,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DQ) {
-            smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_ds, kp);
+            smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_ds, kp);
             ++g_last_launches;
         }
     }

@@ -43,6 +43,10 @@ struct KParams {
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
+#ifdef SMLA_DEBUG_KNOBS
+    int dbg;                  // experiment switches, never set in the shipped build
+    long long* dbg_buf;       // cycle counters written by CTA 0
+#endif
 };
 
 // error codes recorded by bounded waits: 100*kernel + site
@@ -90,16 +94,17 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 //   warps 4-11  gather producers: per 128-key tile nine [128 keys x 64 col] chunks of kv rows picked by
 //               index, copied with 16-byte cp.async into the 128-byte-swizzled layout the UMMA reads
 //               (the TMA gather4 path tops out near 8 B/clk per SM; 256 threads of cp.async reach ~20)
+//   warp 13     second gather path: every third chunk comes through TMA gather4 instead (4 rows per lane),
+//               which adds the TMA unit's ~8 B/clk to what the cp.async threads sustain
 //   warp 12     UMMA issuer (+ TMEM allocation, + the Q / dO chunks of the head group by TMA):
 //               P^T[128 keys, 64 heads] += Kg_chunk . Q_chunk^T  (9 chunks, K = 576)
 //               dP^T                    += Kg_chunk . dO_chunk^T (8 chunks, K = 512)
 //               accumulators double-buffered in TMEM (2 x 128 columns)
 // =============================================================================================
 namespace rc {
-constexpr int kThreads = 416;
+constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kStages = 5;
-constexpr int kLag = 3;                        // cp.async groups a producer thread keeps in flight
 constexpr int kTileKeys = 128;
 constexpr int kChunkBytesA = kTileKeys * 128;  // 16 KB gathered chunk
 constexpr int kChunkBytesB = 64 * 128;         // 8 KB Q / dO chunk (64 heads)
@@ -113,7 +118,7 @@ constexpr int kSmemBytes = kOffMisc + 1024 + 1024;  // + misc + alignment slack
 template <int HP>
 __global__ void __launch_bounds__(rc::kThreads, 1)
 smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                      const KParams p) {
+                      const __grid_constant__ CUtensorMap tm_kv, const KParams p) {
     using namespace rc;
     constexpr int G = HP / 64;
     const int g = blockIdx.x % G;
@@ -142,7 +147,7 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (threadIdx.x == 0) {
         *s_abort = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, kProducerWarps);
+            mbar_init(bar_full + 8 * i, kProducerWarps * 32);
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_qdo, 1);
@@ -169,7 +174,10 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of the tile
         const uint32_t dst0 = s_base + kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
-        int it = 0;
+        // chunks with j % 3 == 0 belong to the TMA warp
+#ifdef SMLA_DEBUG_KNOBS
+        if (!(p.dbg & 8))
+#endif
         for (int tile = 0; tile < n_tiles; ++tile) {
             const char* src[4];
 #pragma unroll
@@ -179,26 +187,54 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 idx = min(max(idx, 0), p.s_kv - 1);   // unused slots gather a real row; their S, dS are forced to 0
                 src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
             }
-            for (int j = 0; j < kQChunks; ++j, ++it) {
+            for (int j = 0; j < kQChunks; ++j) {
+                if (j % 3 == 0) continue;
+                const int it = tile * kQChunks + j;
                 const int s = it % kStages;
                 mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 1);
                 const uint32_t d = dst0 + s * kChunkBytesA;
+#ifdef SMLA_DEBUG_KNOBS
+                if (!(p.dbg & 1))
+#endif
 #pragma unroll
                 for (int i = 0; i < 4; ++i) cp_async16(d + i * 32 * 128, src[i] + j * 128);
-                cp_async_commit();
-                if (it >= kLag) {
-                    cp_async_wait<kLag>();
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full + 8 * ((it - kLag) % kStages));
-                }
+                cp_async_mbar_arrive_noinc(bar_full + 8 * s);   // fires when this thread's copies have landed
             }
         }
-        cp_async_wait<0>();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0)
-            for (int d = (it < kLag ? it : kLag); d >= 1; --d) mbar_arrive(bar_full + 8 * ((it - d) % kStages));
+    } else if (warp == 13) {
+        // ------------------------------------------------------------------ TMA gather4 path (chunks 0, 3, 6)
+        if (lane == 0) tma_prefetch_desc(&tm_kv);
+#ifdef SMLA_DEBUG_KNOBS
+        if (!(p.dbg & 8))
+#endif
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            int r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int key = tile * kTileKeys + lane * 4 + k;
+                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                r[k] = min(max(idx, 0), p.s_kv - 1);
+            }
+            for (int j = 0; j < kQChunks; j += 3) {
+                const int it = tile * kQChunks + j;
+                const int s = it % kStages;
+                mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 6);
+                // the stage barrier counts one arrival per cp.async producer thread; stand in for all of them
+#ifdef SMLA_DEBUG_KNOBS
+                if (p.dbg & 4) {
+                    if (lane == 0) mbar_arrive_n(bar_full + 8 * s, kProducerWarps * 32);
+                    continue;
+                }
+#endif
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar_full + 8 * s, kChunkBytesA);
+                    mbar_arrive_n(bar_full + 8 * s, kProducerWarps * 32 - 1);
+                }
+                __syncwarp();
+                tma_gather4(s_base + kOffRing + s * kChunkBytesA + lane * 512, &tm_kv, 64 * j, r[0], r[1], r[2], r[3],
+                            bar_full + 8 * s);
+            }
+        }
     } else if (warp == 12) {
         // ------------------------------------------------------------------ UMMA issuer
         if (lane == 0) {
@@ -210,17 +246,39 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             for (int j = 0; j < kVChunks; ++j) tma_load_2d(s_base + kOffDO + j * kChunkBytesB, &tm_do, 64 * j, row0, bar_qdo);
 
             constexpr uint32_t idesc = make_idesc_bf16(128, 64, 0, 0);
+#ifdef SMLA_DEBUG_KNOBS
+            long long c_qdo = clock64(), c_tempty = 0, c_full = 0, c_issue = 0, c0;
+#endif
             mbar_wait(bar_qdo, 0, wc, kErrRecompute + 2);
+#ifdef SMLA_DEBUG_KNOBS
+            c_qdo = clock64() - c_qdo;
+            const long long c_start = clock64();
+#endif
             int it = 0;
             for (int tile = 0; tile < n_tiles; ++tile) {
                 const int b = tile & 1;
+#ifdef SMLA_DEBUG_KNOBS
+                c0 = clock64();
+#endif
                 mbar_wait(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 3);
+#ifdef SMLA_DEBUG_KNOBS
+                c_tempty += clock64() - c0;
+#endif
                 tc_fence_after_sync();
                 const uint32_t d_p = tmem + b * 128;
                 const uint32_t d_dp = d_p + 64;
                 for (int j = 0; j < kQChunks; ++j, ++it) {
                     const int s = it % kStages;
+#ifdef SMLA_DEBUG_KNOBS
+                    c0 = clock64();
+                    if (!(p.dbg & 8))
+#endif
                     mbar_wait(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 4);
+#ifdef SMLA_DEBUG_KNOBS
+                    c_full += clock64() - c0;
+                    c0 = clock64();
+#endif
+                    fence_proxy_async_smem();   // cp.async wrote through the generic proxy, the UMMA reads through the async one
                     tc_fence_after_sync();
                     const uint32_t a0 = s_base + kOffRing + s * kChunkBytesA;
                     const uint32_t bq = s_base + kOffQ + j * kChunkBytesB;
@@ -229,13 +287,25 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     for (int k = 0; k < 4; ++k) {
                         const uint64_t ad = make_smem_desc(a0 + 32 * k, 16, 1024, kSwizzle128);
                         umma_ss(d_p, ad, make_smem_desc(bq + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
+#ifdef SMLA_DEBUG_KNOBS
+                        if (!(p.dbg & 16))
+#endif
                         if (j < kVChunks)
                             umma_ss(d_dp, ad, make_smem_desc(bd + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
                     }
                     umma_commit(bar_empty + 8 * s);
+#ifdef SMLA_DEBUG_KNOBS
+                    c_issue += clock64() - c0;
+#endif
                 }
                 umma_commit(bar_tfull + 8 * b);
             }
+#ifdef SMLA_DEBUG_KNOBS
+            if (blockIdx.x == 0 && p.dbg_buf) {
+                p.dbg_buf[0] = c_qdo; p.dbg_buf[1] = c_tempty; p.dbg_buf[2] = c_full; p.dbg_buf[3] = c_issue;
+                p.dbg_buf[4] = clock64() - c_start;
+            }
+#endif
         }
     } else {
         // ------------------------------------------------------------------ softmax gradient
@@ -249,17 +319,34 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int row = quarter * 32 + lane;
+#ifdef SMLA_DEBUG_KNOBS
+        long long s_ldg = 0, s_wait = 0, s_math = 0, s0;
+#endif
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int key = tile * kTileKeys + row;
+#ifdef SMLA_DEBUG_KNOBS
+            s0 = clock64();
+#endif
             const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
             const bool valid = slot_valid(idx, qg, p);
+#ifdef SMLA_DEBUG_KNOBS
+            if (valid) s_ldg += clock64() - s0; else s_ldg += clock64() - s0 + 1;
+            s0 = clock64();
+#endif
             const int b = tile & 1;
             mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 5);
+#ifdef SMLA_DEBUG_KNOBS
+            s_wait += clock64() - s0;
+            s0 = clock64();
+#endif
             tc_fence_after_sync();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * 128;
             const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + 64 * g;
             uint4* s_out = reinterpret_cast<uint4*>(p.s_scr + off);
             uint4* ds_out = reinterpret_cast<uint4*>(p.ds_scr + off);
+#ifdef SMLA_DEBUG_KNOBS
+            if (!(p.dbg & 2))
+#endif
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
                 uint32_t pv[32], dpv[32];
@@ -289,11 +376,250 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+#ifdef SMLA_DEBUG_KNOBS
+            s_math += clock64() - s0;
+#endif
         }
+#ifdef SMLA_DEBUG_KNOBS
+        if (blockIdx.x == 0 && threadIdx.x == 0 && p.dbg_buf) { p.dbg_buf[8] = s_ldg; p.dbg_buf[9] = s_wait; p.dbg_buf[10] = s_math; }
+#endif
     }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 12) tmem_dealloc(tmem, 256);
+}
+
+// =============================================================================================
+// recompute, pair version: one 2-CTA cluster per query, 18 warps per CTA.
+// The pair works on 256-key tiles with cta_group::2 UMMAs of shape M = 256 keys x N = 2*HP:
+//   A  each CTA gathers ITS 128 keys of the tile (every kv row is fetched once per query, not once
+//      per head group), chunk by chunk through a 5-slot ring of [128 keys x 64 col] chunks;
+//   B  each CTA holds the Q and dO rows of ITS half of the heads, stored per column chunk as
+//      [Q_j | dO_j] so that one UMMA of N = 2*HP yields P^T and dP^T side by side
+//      (chunk 8 has no V columns: its dO half is a block of zeros);
+//   D  each CTA ends up with [its 128 keys] x [P^T | dP^T of all heads] in its own TMEM, columns
+//      ordered (head half 0: P, dP), (head half 1: P, dP); two buffers.
+//   warps 0-7   softmax-gradient on the CTA's own keys: warp w -> TMEM lane quarter w % 4, head half w / 4
+//   warps 8-15  gather producers (cp.async 16 B, swizzled); completion arrives on the slot's mbarrier
+//   warp 16     TMA of the CTA's Q / dO chunks; in the even CTA also the UMMA issuer for the pair
+//   warp 17     odd CTA only: forwards "my slot is full" to the even CTA (cp.async cannot signal remotely)
+// Slot-free and accumulator-ready signals are tcgen05.commit arrivals delivered to both CTAs.
+// =============================================================================================
+namespace rp {
+constexpr int kThreads = 576;
+constexpr int kProducerThreads = 256;
+constexpr int kStages = 5;
+constexpr int kTileKeys = 256;             // per pair; 128 per CTA
+constexpr int kChunkA = 128 * 128;         // 16 KB gathered chunk
+template <int HP> struct Cfg {
+    static constexpr int NH = HP / 2;                  // heads whose Q / dO rows this CTA holds
+    static constexpr int kBHalf = NH * 128;            // one [NH heads x 64 col] chunk
+    static constexpr int kBChunk = 2 * kBHalf;         // stacked [Q_j | dO_j]
+    static constexpr int kOffB = 0;
+    static constexpr int kOffRing = kQChunks * kBChunk;
+    static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
+    static constexpr int kSmemBytes = kOffMisc + 1024 + 256 + 1024;   // lse/delta + barriers + alignment slack
+    static constexpr int kAccCols = 2 * HP;            // one accumulator buffer
+    static constexpr int kTmemCols = 4 * HP;           // two buffers: 512 (HP 128) or 256 (HP 64)
+};
+}  // namespace rp
+
+template <int HP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(rp::kThreads, 1)
+smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                           const KParams p) {
+    using namespace rp;
+    using C = Cfg<HP>;
+    constexpr int NH = C::NH;
+    const uint32_t rank = cluster_ctarank();
+    const int ql = blockIdx.x >> 1;
+    const int qg = p.q0 + ql;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t s_base = smem_u32(smem);
+    uint8_t* misc = smem + C::kOffMisc;
+    float* lse_s = reinterpret_cast<float*>(misc);          // [HP] base-2 lse, +inf for padded heads
+    float* delta_s = lse_s + HP;                            // [HP]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 1024);
+    const uint32_t bar_full = smem_u32(bars);               // [kStages] this CTA's gathered chunk landed
+    const uint32_t bar_empty = bar_full + 8 * kStages;      // [kStages] pair UMMAs reading the slot finished
+    const uint32_t bar_pfull = bar_empty + 8 * kStages;     // [kStages] (even CTA) the odd CTA's chunk landed
+    const uint32_t bar_qdo = bar_pfull + 8 * kStages;       // 1
+    const uint32_t bar_tfull = bar_qdo + 8;                 // [2] accumulator buffer complete
+    const uint32_t bar_tempty = bar_tfull + 16;             // [2] (even CTA) both CTAs have read the buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (3 * kStages + 5));
+    volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const WaitCtx wc{p.g_err, s_abort};
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(bar_full + 8 * i, kProducerThreads);
+            mbar_init(bar_empty + 8 * i, 1);
+            mbar_init(bar_pfull + 8 * i, 1);
+        }
+        mbar_init(bar_qdo, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + 8 * i, 1);
+            mbar_init(bar_tempty + 8 * i, 16);   // 8 softmax warps in each CTA
+        }
+        fence_mbar_init();
+    }
+    {   // zero block standing in for the dO half of column chunk 8
+        uint4* z = reinterpret_cast<uint4*>(smem + C::kOffB + 8 * C::kBChunk + C::kBHalf);
+        for (int i = threadIdx.x; i < C::kBHalf / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
+        fence_proxy_async_smem();
+    }
+    if (warp == 16) {
+        tmem_alloc_2cta(smem_u32(tmem_slot), C::kTmemCols);
+        tmem_relinquish_2cta();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();          // barriers of both CTAs are initialised before anyone signals across
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int n_tiles = p.topk_pad / kTileKeys;
+    const int n_chunks = n_tiles * kQChunks;
+
+    if (warp >= 8 && warp < 16) {
+        // ------------------------------------------------------------------ gather producers
+        const int pt = threadIdx.x - 256;   // 0..255
+        const int u = pt & 7;               // 16-byte unit inside a 128-byte chunk row
+        const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of this CTA's 128 keys
+        const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
+        const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
+        int it = 0;
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const char* src[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = tile * kTileKeys + rank * 128 + r0 + 32 * i;
+                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                idx = min(max(idx, 0), p.s_kv - 1);   // unused slots gather a real row; their S, dS are forced to 0
+                src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
+            }
+            for (int j = 0; j < kQChunks; ++j, ++it) {
+                const int s = it % kStages;
+                mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 11);
+                const uint32_t d = dst0 + s * kChunkA;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) cp_async16(d + i * 32 * 128, src[i] + j * 128);
+                cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 16) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_do);
+            mbar_arrive_expect_tx(bar_qdo, (kQChunks + kVChunks) * C::kBHalf);
+            const int row0 = qg * p.h_q + NH * rank;
+            for (int j = 0; j < kQChunks; ++j) tma_load_2d(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_qdo);
+            for (int j = 0; j < kVChunks; ++j)
+                tma_load_2d(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo);
+            if (rank == 0) {
+                // -------------------------------------------------------------- UMMA issuer for the pair
+                constexpr uint32_t idesc = make_idesc_bf16(256, 2 * HP, 0, 0);
+                mbar_wait(bar_qdo, 0, wc, kErrRecompute + 12);
+                int it = 0;
+                for (int tile = 0; tile < n_tiles; ++tile) {
+                    const int b = tile & 1;
+                    mbar_wait(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
+                    tc_fence_after_sync();
+                    const uint32_t d = tmem + b * C::kAccCols;
+                    for (int j = 0; j < kQChunks; ++j, ++it) {
+                        const int s = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        mbar_wait(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
+                        mbar_wait(bar_pfull + 8 * s, ph, wc, kErrRecompute + 15);
+                        fence_proxy_async_smem();   // cp.async wrote through the generic proxy
+                        tc_fence_after_sync();
+                        const uint32_t a0 = s_base + C::kOffRing + s * kChunkA;
+                        const uint32_t b0 = s_base + C::kOffB + j * C::kBChunk;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_ss_2cta(d, make_smem_desc(a0 + 32 * k, 16, 1024, kSwizzle128),
+                                         make_smem_desc(b0 + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
+                        umma_commit_2cta(bar_empty + 8 * s);
+                        umma_commit_2cta(map_to_cta(bar_empty + 8 * s, 1));
+                    }
+                    umma_commit_2cta(bar_tfull + 8 * b);
+                    umma_commit_2cta(map_to_cta(bar_tfull + 8 * b, 1));
+                }
+            }
+        }
+    } else if (warp == 17) {
+        if (lane == 0 && rank == 1) {
+            // ---------------------------------------------------------------- forward slot-full to the even CTA
+            mbar_wait(bar_qdo, 0, wc, kErrRecompute + 16);   // Q / dO of this CTA are part of what "full" promises
+            for (int it = 0; it < n_chunks; ++it) {
+                const int s = it % kStages;
+                mbar_wait(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 17);
+                fence_proxy_async_smem();
+                mbar_arrive_cluster(map_to_cta(bar_pfull + 8 * s, 0));
+            }
+        } else if (lane == 0) {
+            // the even CTA's own chunks need no forwarding; complete its pfull phases locally? no: pfull counts
+            // only the odd CTA's arrival, nothing to do here
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax gradient (own 128 keys)
+        const int quarter = warp & 3;
+        const int g = warp >> 2;            // head half
+        for (int h = threadIdx.x; h < HP; h += 256) {
+            const bool hv = h < p.h_q;
+            lse_s[h] = hv ? p.lse[static_cast<size_t>(qg) * p.h_q + h] * p.lse_mult : __int_as_float(0x7f800000);
+            delta_s[h] = hv ? p.delta[static_cast<size_t>(qg) * p.h_q + h] : 0.f;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const int row = quarter * 32 + lane;
+        const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const int key = tile * kTileKeys + rank * 128 + row;
+            const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+            const bool valid = slot_valid(idx, qg, p);
+            const int b = tile & 1;
+            mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 18);
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
+            const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
+            __nv_bfloat16* s_out = p.s_scr + off;
+            __nv_bfloat16* ds_out = p.ds_scr + off;
+#pragma unroll 1
+            for (int c0 = 0; c0 < NH; c0 += 16) {
+                uint32_t pv[16], dpv[16];
+                tmem_ld_32x16(taddr + c0, pv);
+                tmem_ld_32x16(taddr + NH + c0, dpv);
+                tmem_ld_wait();
+                uint32_t so[8], dso[8];
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    float sv[2], dsv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int h = g * NH + c0 + c + e;
+                        const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c + e]), p.scale_log2e, -lse_s[h])) : 0.f;
+                        sv[e] = sx;
+                        dsv[e] = valid ? sx * (__uint_as_float(dpv[c + e]) - delta_s[h]) * p.sm_scale : 0.f;
+                    }
+                    so[c >> 1] = pack_bf16x2(sv[0], sv[1]);
+                    dso[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+                }
+                st_global_v8(s_out + c0, so);
+                st_global_v8(ds_out + c0, dso);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
+    if (warp == 16) tmem_dealloc_2cta(tmem, C::kTmemCols);
 }
 
 // =============================================================================================
@@ -484,16 +810,17 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // dq: one CTA per (query, d-part); same d split as dkv; 13 warps.
 //   warps 0-3   epilogue: TMEM -> bf16 -> dQ[q, head, d]
 //   warps 4-11  producers: per 64-key tile the part's columns of the kv rows picked by index (16-byte
-//               cp.async into the swizzled layout); thread 128 also issues the TMA load of the dS tile
+//               cp.async into the swizzled layout)
+//   warp 13     TMA: the dS scratch tile, and the first two column chunks of the tile through gather4
 //   warp 12     UMMA issuer: acc[blk][128 d, HP heads] += Kg^T . dS^T  (both operands MN-major:
 //               the key index is the contraction and runs along shared-memory rows)
 // =============================================================================================
 namespace dq {
-constexpr int kThreads = 416;
+constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
 constexpr int kStages = 3;
-constexpr int kLag = 2;
+constexpr int kTmaChunks = 2;   // column chunks of every tile that come through TMA gather4 instead of cp.async
 template <int HP> struct Cfg {
     static constexpr int kKgBytes = 5 * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
@@ -506,7 +833,7 @@ template <int HP> struct Cfg {
 
 template <int HP>
 __global__ void __launch_bounds__(dq::kThreads, 1)
-smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
+smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
     using C = Cfg<HP>;
     const int part = blockIdx.x & 1;
@@ -532,7 +859,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     if (threadIdx.x == 0) {
         *s_abort = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, kProducerWarps + 1);   // 8 producer warps + the TMA expect_tx arrival
+            mbar_init(bar_full + 8 * i, kProducerWarps * 32 + 1);   // cp.async threads + the TMA expect_tx arrival
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_acc, 1);
@@ -554,7 +881,6 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         const int r0 = pt >> 3;             // rows r0 and r0+32 of the tile
         const uint32_t dst0 = s_base + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + chunk0 * 128 + u * 16;
-        if (pt == 0) tma_prefetch_desc(&tm_ds);
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile % kStages;
             const char* src[2];
@@ -567,35 +893,49 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1);
             const uint32_t d = dst0 + s * C::kStage;
-            if (pt == 0) {
-                mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes);
-                const int row = ql * p.topk_pad + tile * kTileKeys;
-                for (int c = 0; c < HP / 64; ++c)
-                    tma_load_2d(s_base + s * C::kStage + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
-            }
-            for (int c = 0; c < n_ch; ++c) {
+            for (int c = kTmaChunks; c < n_ch; ++c) {
                 cp_async16(d + c * 8192, src[0] + c * 128);
                 cp_async16(d + c * 8192 + 32 * 128, src[1] + c * 128);
             }
-            cp_async_commit();
-            if (tile >= kLag) {
-                cp_async_wait<kLag>();
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full + 8 * ((tile - kLag) % kStages));
+            cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+        }
+    } else if (warp == 13) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_ds);
+            tma_prefetch_desc(&tm_kv);
+        }
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            const int s = tile % kStages;
+            int r[4] = {0, 0, 0, 0};
+            if (lane < 16) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int key = tile * kTileKeys + lane * 4 + k;
+                    int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
+                    r[k] = min(max(idx, 0), p.s_kv - 1);
+                }
+            }
+            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4);
+            const uint32_t dst = s_base + s * C::kStage;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
+                const int row = ql * p.topk_pad + tile * kTileKeys;
+                for (int c = 0; c < HP / 64; ++c) tma_load_2d(dst + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
+            }
+            __syncwarp();
+            if (lane < 16) {
+                for (int c = 0; c < kTmaChunks; ++c)
+                    tma_gather4(dst + c * 8192 + lane * 512, &tm_kv, 64 * (chunk0 + c), r[0], r[1], r[2], r[3],
+                                bar_full + 8 * s);
             }
         }
-        cp_async_wait<0>();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0)
-            for (int d = (n_tiles < kLag ? n_tiles : kLag); d >= 1; --d) mbar_arrive(bar_full + 8 * ((n_tiles - d) % kStages));
     } else if (warp == 12) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_bf16(128, HP, 1, 1);
             for (int tile = 0; tile < n_tiles; ++tile) {
                 const int s = tile % kStages;
                 mbar_wait(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
+                fence_proxy_async_smem();
                 tc_fence_after_sync();
                 const uint32_t kg = s_base + s * C::kStage;
                 const uint32_t ds = kg + C::kKgBytes;
