@@ -131,6 +131,10 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
     ok &= make_map_2d(&tm_dohp, p->dO, kDV, qrows, kDV * 2, 64, HP);
     ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
+    // S / dS scratch: the dkv kernel loads [128 keys x 64 heads] boxes, the dq kernel [64 keys x 64 heads]
+    CUtensorMap tm_s128, tm_ds128;
+    ok &= make_map_2d(&tm_s128, s_scr, HP, srows, HP * 2, 64, 128);
+    ok &= make_map_2d(&tm_ds128, ds_scr, HP, srows, HP * 2, 64, 128);
     ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
     ok &= make_map_2d(&tm_ds, ds_scr, HP, srows, HP * 2, 64, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
@@ -180,7 +184,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DKV) {
-            smla_dkv_kernel<HP><<<nq * 2, dk::kThreads, dk::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
+            smla_dkv_kernel<HP><<<nq * 2, dk::kThreads, dk::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s128, tm_ds128, kp);
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DQ) {

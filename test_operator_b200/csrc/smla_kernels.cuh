@@ -506,6 +506,9 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const int s = it % kStages;
                 mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 11);
                 const uint32_t d = dst0 + s * kChunkA;
+#ifdef SMLA_DEBUG_KNOBS
+                if (!(p.dbg & 1))
+#endif
 #pragma unroll
                 for (int i = 0; i < 4; ++i) cp_async16(d + i * 32 * 128, src[i] + j * 128);
                 cp_async_mbar_arrive_noinc(bar_full + 8 * s);
@@ -523,32 +526,68 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             if (rank == 0) {
                 // -------------------------------------------------------------- UMMA issuer for the pair
                 constexpr uint32_t idesc = make_idesc_bf16(256, 2 * HP, 0, 0);
+#ifdef SMLA_DEBUG_KNOBS
+                long long k_wait = 0, k_fence = 0, k_issue = 0, k_commit = 0, k_tempty = 0, k_t0 = 0, k_total = 0;
+#endif
                 mbar_wait(bar_qdo, 0, wc, kErrRecompute + 12);
                 int it = 0;
                 for (int tile = 0; tile < n_tiles; ++tile) {
                     const int b = tile & 1;
+#ifdef SMLA_DEBUG_KNOBS
+                    long long c1 = clock64();
+#endif
                     mbar_wait(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
+#ifdef SMLA_DEBUG_KNOBS
+                    k_tempty += clock64() - c1; if (tile == 0) k_t0 = clock64(); if (tile == n_tiles - 1) k_total = clock64() - k_t0;
+#endif
                     tc_fence_after_sync();
                     const uint32_t d = tmem + b * C::kAccCols;
                     for (int j = 0; j < kQChunks; ++j, ++it) {
                         const int s = it % kStages;
                         const uint32_t ph = (it / kStages) & 1;
+#ifdef SMLA_DEBUG_KNOBS
+                        long long c0 = clock64();
+                        if (!(p.dbg & 8)) {
+#endif
                         mbar_wait(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
                         mbar_wait(bar_pfull + 8 * s, ph, wc, kErrRecompute + 15);
+#ifdef SMLA_DEBUG_KNOBS
+                        }
+                        k_wait += clock64() - c0;
+                        c0 = clock64();
+                        if (!(p.dbg & 32))
+#endif
                         fence_proxy_async_smem();   // cp.async wrote through the generic proxy
                         tc_fence_after_sync();
+#ifdef SMLA_DEBUG_KNOBS
+                        k_fence += clock64() - c0;
+                        c0 = clock64();
+#endif
                         const uint32_t a0 = s_base + C::kOffRing + s * kChunkA;
                         const uint32_t b0 = s_base + C::kOffB + j * C::kBChunk;
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             umma_ss_2cta(d, make_smem_desc(a0 + 32 * k, 16, 1024, kSwizzle128),
                                          make_smem_desc(b0 + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
+#ifdef SMLA_DEBUG_KNOBS
+                        k_issue += clock64() - c0;
+                        c0 = clock64();
+#endif
                         umma_commit_2cta(bar_empty + 8 * s);
                         umma_commit_2cta(map_to_cta(bar_empty + 8 * s, 1));
+#ifdef SMLA_DEBUG_KNOBS
+                        k_commit += clock64() - c0;
+#endif
                     }
                     umma_commit_2cta(bar_tfull + 8 * b);
                     umma_commit_2cta(map_to_cta(bar_tfull + 8 * b, 1));
                 }
+#ifdef SMLA_DEBUG_KNOBS
+                if (blockIdx.x == 0) {
+                    p.dbg_buf[0] = k_wait; p.dbg_buf[1] = k_fence; p.dbg_buf[2] = k_tempty; p.dbg_buf[5] = k_issue;
+                    p.dbg_buf[6] = k_commit; p.dbg_buf[4] = k_total;
+                }
+#endif
             }
         }
     } else if (warp == 17) {
@@ -588,6 +627,9 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
             __nv_bfloat16* s_out = p.s_scr + off;
             __nv_bfloat16* ds_out = p.ds_scr + off;
+#ifdef SMLA_DEBUG_KNOBS
+            if (!(p.dbg & 2))
+#endif
 #pragma unroll 1
             for (int c0 = 0; c0 < NH; c0 += 16) {
                 uint32_t pv[16], dpv[16];
@@ -626,29 +668,30 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 // dkv: one CTA per (query, d-part).  d-part 0 owns columns [0,320), part 1 owns [320,576).
 //   resident   Q^T and dO^T of the part: chunks [HP heads x 64 d] read MN-major as the A operand
 //              (M = d, 128 rows = two adjacent chunks, K = heads)
-//   warp 0     producer: resident chunks once, then per 64-key tile the S and dS scratch tiles
-//              [64 keys x HP heads] (B operand, K-major)
-//   warp 1     UMMA issuer: acc[blk][128 d, 64 keys] = dO^T . S + Q^T . dS, double-buffered in TMEM
-//   warps 2-9  drain: thread = d row, each warp owns 32 d rows x 32 keys of a tile; one fp32 reduction
-//              per key, 32 lanes -> 128 contiguous bytes
+//   warp 0     producer: resident chunks once, then per 128-key tile the S and dS scratch tiles
+//              [128 keys x HP heads] (B operand, K-major); one shared-memory stage
+//   warp 1     UMMA issuer: unit = (tile, block of 128 d rows): acc[128 d, 128 keys] = dO^T . S + Q^T . dS
+//              into a ring of four 128-column TMEM units, so the MMAs run ahead of the drain
+//   warps 2-9  drain: thread = d row, each warp owns 32 d rows x 64 keys of a unit; one fp32 reduction
+//              per key, 32 lanes -> 128 contiguous bytes of dKV
 // Part 0's third block has 64 real rows (d 256..319); its upper 64 rows read whatever follows
 // in shared memory and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
 // =============================================================================================
 namespace dk {
 constexpr int kThreads = 320;   // warp 0 producer, warp 1 UMMA issuer, warps 2-9 drain
-constexpr int kTileKeys = 64;
+constexpr int kTileKeys = 128;
 constexpr int kResChunks = 5;
+constexpr int kUnits = 4;       // TMEM accumulator ring: 4 x 128 columns
 template <int HP> struct Cfg {
     static constexpr int kChunk = HP * 128;                 // resident chunk bytes
-    static constexpr int kTileMat = (HP / 64) * 8192;       // one S (or dS) tile
+    static constexpr int kTileMat = (HP / 64) * 16384;      // one S (or dS) tile: [128 keys x HP heads]
     static constexpr int kStage = 2 * kTileMat;
     static constexpr int kOffQ = 0;
     static constexpr int kOffDO = kResChunks * kChunk;
     static constexpr int kOffStage = 2 * kResChunks * kChunk;
-    static constexpr int kOffMisc = kOffStage + 2 * kStage;
-    static constexpr int kOffIdx = kOffMisc + 128;          // 8 drain warps x 32 int
-    static constexpr int kSmemBytes = kOffMisc + 128 + 1024 + 1024;
-    static constexpr int kAccCols = 192;                    // 3 blocks x 64 keys per buffer
+    static constexpr int kOffMisc = kOffStage + kStage;
+    static constexpr int kOffIdx = kOffMisc + 128;          // 8 drain warps x 64 int
+    static constexpr int kSmemBytes = kOffMisc + 128 + 2048 + 896;   // all of the 227 KB; 896 B alignment slack
 };
 }  // namespace dk
 
@@ -671,25 +714,29 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t s_base = smem_u32(smem);
+    if (smem - smem_raw > 896) {   // the carve-up below would run past the allocation (uniform across the CTA)
+        if (threadIdx.x == 0) atomicCAS(p.g_err, 0, kErrDkv + 9);
+        return;
+    }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffMisc);
-    const uint32_t bar_full = smem_u32(bars);      // [2]
-    const uint32_t bar_empty = bar_full + 16;      // [2]
-    const uint32_t bar_res = bar_empty + 16;       // 1
-    const uint32_t bar_afull = bar_res + 8;        // [2]
-    const uint32_t bar_aempty = bar_afull + 16;    // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 80);
+    const uint32_t bar_sfull = smem_u32(bars);          // 1  S/dS tile landed
+    const uint32_t bar_sempty = bar_sfull + 8;          // 1  all UMMAs of the tile finished
+    const uint32_t bar_res = bar_sempty + 8;            // 1
+    const uint32_t bar_ufull = bar_res + 8;             // [kUnits]
+    const uint32_t bar_uempty = bar_ufull + 8 * kUnits; // [kUnits]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (3 + 2 * kUnits));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const WaitCtx wc{p.g_err, s_abort};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_full + 8 * i, 1);
-            mbar_init(bar_empty + 8 * i, 1);
-            mbar_init(bar_afull + 8 * i, 1);
-            mbar_init(bar_aempty + 8 * i, 8);
-        }
+        mbar_init(bar_sfull, 1);
+        mbar_init(bar_sempty, 1);
         mbar_init(bar_res, 1);
+        for (int i = 0; i < kUnits; ++i) {
+            mbar_init(bar_ufull + 8 * i, 1);
+            mbar_init(bar_uempty + 8 * i, 8);
+        }
         fence_mbar_init();
     }
     if (part == 1) {  // zero chunk standing in for dO columns 512..575
@@ -720,85 +767,89 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int j = 0; j < n_do; ++j)
                 tma_load_2d(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res);
             for (int tile = 0; tile < n_tiles; ++tile) {
-                const int s = tile & 1;
-                mbar_wait(bar_empty + 8 * s, ((tile >> 1) & 1) ^ 1, wc, kErrDkv + 1);
-                mbar_arrive_expect_tx(bar_full + 8 * s, C::kStage);
+                mbar_wait(bar_sempty, (tile & 1) ^ 1, wc, kErrDkv + 1);
+                mbar_arrive_expect_tx(bar_sfull, C::kStage);
                 const int row = ql * p.topk_pad + tile * kTileKeys;
-                const uint32_t dst = s_base + C::kOffStage + s * C::kStage;
-                for (int c = 0; c < HP / 64; ++c) {
-                    tma_load_2d(dst + c * 8192, &tm_s, 64 * c, row, bar_full + 8 * s);
-                    tma_load_2d(dst + C::kTileMat + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
+                const uint32_t dst = s_base + C::kOffStage;
+                for (int c = 0; c < HP / 64; ++c) {     // box = [128 keys x 64 heads]
+                    tma_load_2d(dst + c * 16384, &tm_s, 64 * c, row, bar_sfull);
+                    tma_load_2d(dst + C::kTileMat + c * 16384, &tm_ds, 64 * c, row, bar_sfull);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 0);  // A MN-major (d contiguous), B K-major
+            constexpr uint32_t idesc = make_idesc_bf16(128, 128, 1, 0);  // A MN-major (d contiguous), B K-major
             mbar_wait(bar_res, 0, wc, kErrDkv + 2);
+            const uint32_t st_s = s_base + C::kOffStage;
+            const uint32_t st_ds = st_s + C::kTileMat;
+            int unit = 0;
             for (int tile = 0; tile < n_tiles; ++tile) {
-                const int s = tile & 1;
-                const uint32_t ph = (tile >> 1) & 1;
-                mbar_wait(bar_aempty + 8 * s, ph ^ 1, wc, kErrDkv + 3);
-                mbar_wait(bar_full + 8 * s, ph, wc, kErrDkv + 4);
-                tc_fence_after_sync();
-                const uint32_t st_s = s_base + C::kOffStage + s * C::kStage;
-                const uint32_t st_ds = st_s + C::kTileMat;
-                for (int blk = 0; blk < n_blk; ++blk) {
-                    const uint32_t d = tmem + s * C::kAccCols + blk * 64;
+                mbar_wait(bar_sfull, tile & 1, wc, kErrDkv + 4);
+                for (int blk = 0; blk < n_blk; ++blk, ++unit) {
+                    const int us = unit % kUnits;
+                    mbar_wait(bar_uempty + 8 * us, ((unit / kUnits) & 1) ^ 1, wc, kErrDkv + 3);
+                    tc_fence_after_sync();
+                    const uint32_t d = tmem + us * 128;
                     const uint32_t a_do = s_base + C::kOffDO + 2 * blk * C::kChunk;
                     const uint32_t a_q = s_base + C::kOffQ + 2 * blk * C::kChunk;
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
-                                make_smem_desc(st_s + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
+                                make_smem_desc(st_s + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
                                 ks != 0);
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_q + ks * 2048, C::kChunk, 1024, kSwizzle128),
-                                make_smem_desc(st_ds + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
+                                make_smem_desc(st_ds + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
                                 1);
+                    umma_commit(bar_ufull + 8 * us);
                 }
-                umma_commit(bar_empty + 8 * s);
-                umma_commit(bar_afull + 8 * s);
+                umma_commit(bar_sempty);
             }
         }
     } else {
         const int quarter = warp & 3;
-        const int e = (warp - 2) >> 2;          // which 32 keys of the 64-key tile this warp scatters
+        const int e = (warp - 2) >> 2;          // which 64 keys of the 128-key tile this warp scatters
         const int d_part0 = chunk0 * 64;
-        int* idx_s = reinterpret_cast<int*>(smem + C::kOffIdx) + (warp - 2) * 32;
+        int* idx_s = reinterpret_cast<int*>(smem + C::kOffIdx) + (warp - 2) * 64;
+        int unit = 0;
         for (int tile = 0; tile < n_tiles; ++tile) {
-            const int s = tile & 1;
-            {
-                const int key = tile * kTileKeys + 32 * e + lane;
-                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                __syncwarp();
-                idx_s[lane] = slot_valid(idx, qg, p) ? idx : -1;
-                __syncwarp();
-            }
-            int ix[32];
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-                const int4 t = reinterpret_cast<const int4*>(idx_s)[v];
-                ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
-            }
-            mbar_wait(bar_afull + 8 * s, (tile >> 1) & 1, wc, kErrDkv + 5);
-            tc_fence_after_sync();
-            for (int blk = 0; blk < n_blk; ++blk) {
-                if (part == 0 && blk == 2 && quarter >= 2) continue;  // padded rows
-                float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane;
-                const uint32_t taddr =
-                    tmem + (static_cast<uint32_t>(quarter * 32) << 16) + s * C::kAccCols + blk * 64 + 32 * e;
-                uint32_t r[32];
-                tmem_ld_32x32(taddr, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (ix[j] >= 0) red_add_f32(out + static_cast<size_t>(ix[j]) * kDQK, __uint_as_float(r[j]));
-            }
-            tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_aempty + 8 * s);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int key = tile * kTileKeys + 64 * e + 32 * i + lane;
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                idx_s[32 * i + lane] = slot_valid(idx, qg, p) ? idx : -1;
+            }
+            __syncwarp();
+            for (int blk = 0; blk < n_blk; ++blk, ++unit) {
+                const int us = unit % kUnits;
+                mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5);
+                tc_fence_after_sync();
+                if (!(part == 0 && blk == 2 && quarter >= 2)) {   // padded rows are never drained
+                    float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane;
+                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(taddr + 32 * i, r);
+                        int ix[32];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
+                            ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
+                        }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (ix[j] >= 0) red_add_f32(out + static_cast<size_t>(ix[j]) * kDQK, __uint_as_float(r[j]));
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_uempty + 8 * us);
+            }
         }
     }
     tc_fence_before_sync();
@@ -820,7 +871,7 @@ constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
 constexpr int kStages = 3;
-constexpr int kTmaChunks = 2;   // column chunks of every tile that come through TMA gather4 instead of cp.async
+constexpr int kTmaChunks = 0;   // column chunks of a tile routed through TMA gather4 instead of cp.async (measured slower)
 template <int HP> struct Cfg {
     static constexpr int kKgBytes = 5 * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
