@@ -492,6 +492,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of this CTA's 128 keys
         const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
+        const uint64_t pol_keep = l2_policy_evict_last();
         int it = 0;
         for (int tile = 0; tile < n_tiles; ++tile) {
             const char* src[4];
@@ -510,7 +511,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 if (!(p.dbg & 1))
 #endif
 #pragma unroll
-                for (int i = 0; i < 4; ++i) cp_async16(d + i * 32 * 128, src[i] + j * 128);
+                for (int i = 0; i < 4; ++i) cp_async16_hint(d + i * 32 * 128, src[i] + j * 128, pol_keep);
                 cp_async_mbar_arrive_noinc(bar_full + 8 * s);
             }
         }
@@ -520,9 +521,11 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             tma_prefetch_desc(&tm_do);
             mbar_arrive_expect_tx(bar_qdo, (kQChunks + kVChunks) * C::kBHalf);
             const int row0 = qg * p.h_q + NH * rank;
-            for (int j = 0; j < kQChunks; ++j) tma_load_2d(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_qdo);
+            const uint64_t pol_stream = l2_policy_evict_first();
+            for (int j = 0; j < kQChunks; ++j)
+                tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_qdo, pol_stream);
             for (int j = 0; j < kVChunks; ++j)
-                tma_load_2d(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo);
+                tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo, pol_stream);
             if (rank == 0) {
                 // -------------------------------------------------------------- UMMA issuer for the pair
                 constexpr uint32_t idesc = make_idesc_bf16(256, 2 * HP, 0, 0);
@@ -616,6 +619,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const int row = quarter * 32 + lane;
         const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
+        const uint64_t pol_stream = l2_policy_evict_first();
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int key = tile * kTileKeys + rank * 128 + row;
             const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
@@ -650,8 +654,8 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     so[c >> 1] = pack_bf16x2(sv[0], sv[1]);
                     dso[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
                 }
-                st_global_v8(s_out + c0, so);
-                st_global_v8(ds_out + c0, dso);
+                st_global_v8_hint(s_out + c0, so, pol_stream);
+                st_global_v8_hint(ds_out + c0, dso, pol_stream);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -762,18 +766,19 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tma_prefetch_desc(&tm_ds);
             mbar_arrive_expect_tx(bar_res, (n_q + n_do) * C::kChunk);
             const int row0 = qg * p.h_q;
+            const uint64_t pol_stream = l2_policy_evict_first();
             for (int j = 0; j < n_q; ++j)
-                tma_load_2d(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * (chunk0 + j), row0, bar_res);
+                tma_load_2d_hint(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * (chunk0 + j), row0, bar_res, pol_stream);
             for (int j = 0; j < n_do; ++j)
-                tma_load_2d(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res);
+                tma_load_2d_hint(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res, pol_stream);
             for (int tile = 0; tile < n_tiles; ++tile) {
                 mbar_wait(bar_sempty, (tile & 1) ^ 1, wc, kErrDkv + 1);
                 mbar_arrive_expect_tx(bar_sfull, C::kStage);
                 const int row = ql * p.topk_pad + tile * kTileKeys;
                 const uint32_t dst = s_base + C::kOffStage;
                 for (int c = 0; c < HP / 64; ++c) {     // box = [128 keys x 64 heads]
-                    tma_load_2d(dst + c * 16384, &tm_s, 64 * c, row, bar_sfull);
-                    tma_load_2d(dst + C::kTileMat + c * 16384, &tm_ds, 64 * c, row, bar_sfull);
+                    tma_load_2d_hint(dst + c * 16384, &tm_s, 64 * c, row, bar_sfull, pol_stream);
+                    tma_load_2d_hint(dst + C::kTileMat + c * 16384, &tm_ds, 64 * c, row, bar_sfull, pol_stream);
                 }
             }
         }
@@ -932,6 +937,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         const int r0 = pt >> 3;             // rows r0 and r0+32 of the tile
         const uint32_t dst0 = s_base + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + chunk0 * 128 + u * 16;
+        const uint64_t pol_keep = l2_policy_evict_last();
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile % kStages;
             const char* src[2];
@@ -945,8 +951,8 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1);
             const uint32_t d = dst0 + s * C::kStage;
             for (int c = kTmaChunks; c < n_ch; ++c) {
-                cp_async16(d + c * 8192, src[0] + c * 128);
-                cp_async16(d + c * 8192 + 32 * 128, src[1] + c * 128);
+                cp_async16_hint(d + c * 8192, src[0] + c * 128, pol_keep);
+                cp_async16_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, pol_keep);
             }
             cp_async_mbar_arrive_noinc(bar_full + 8 * s);
         }
@@ -955,6 +961,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
             tma_prefetch_desc(&tm_ds);
             tma_prefetch_desc(&tm_kv);
         }
+        const uint64_t pol_stream = l2_policy_evict_first();
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile % kStages;
             int r[4] = {0, 0, 0, 0};
@@ -971,7 +978,8 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
                 const int row = ql * p.topk_pad + tile * kTileKeys;
-                for (int c = 0; c < HP / 64; ++c) tma_load_2d(dst + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s);
+                for (int c = 0; c < HP / 64; ++c)
+                    tma_load_2d_hint(dst + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s, pol_stream);
             }
             __syncwarp();
             if (lane < 16) {
