@@ -47,12 +47,48 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe: returns at once, so a spin on it reacts within tens of cycles, whereas try_wait may
+// park the warp and wake it late.  Costs issue slots: only for the few latency-critical waiters.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __noinline__ bool mbar_spin_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
+    const long long t0 = clock64();
+    int it = 0;
+    while (true) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((++it & 255) == 0) {
+            if (*ctx.s_abort) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *ctx.s_abort = 1;
+                atomicCAS(ctx.g_err, 0, code);
+                return false;
+            }
+        }
+    }
+}
+// Bounded low-latency wait (hot spin).
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    return mbar_spin_slow(bar, parity, ctx, code);
+}
 // Bounded wait.  Returns false if it gave up (error `code` recorded) or the CTA is aborting.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
+// `sleep_ns` > 0 makes the waiter yield its issue slots between polls: many warps spinning on barriers
+// otherwise starve the single thread that issues the UMMAs of the scheduler they share.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code, unsigned sleep_ns) {
     const long long t0 = clock64();
     int it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((++it & 31) == 0) {
             if (*ctx.s_abort) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
@@ -63,9 +99,10 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const
         }
     }
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code,
+                                          unsigned sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, ctx, code);
+    return mbar_wait_slow(bar, parity, ctx, code, sleep_ns);
 }
 
 // ---- proxies / fences -------------------------------------------------------------------------
@@ -254,6 +291,13 @@ __device__ __forceinline__ void umma_ss_2cta(uint32_t d_tmem, uint64_t a_desc, u
 // Arrive on `bar` (local, or the peer's through map_to_cta) once the pair UMMAs issued so far have finished.
 __device__ __forceinline__ void umma_commit_2cta(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Same, delivered to the barrier at this shared-memory offset in every CTA of `cta_mask` (bit per cluster rank).
+// This is an mbarrier arrival, not a data transfer.
+__device__ __forceinline__ void umma_commit_2cta_mask(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(

@@ -165,9 +165,9 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     kp.lse_mult = p->lse_is_base2 ? 1.0f : 1.4426950408889634f;
     kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
     kp.q_start = kp.causal ? p->q_start_index_s : 0;
-#ifdef SMLA_DEBUG_KNOBS
-    kp.dbg = getenv("SMLA_DBG") ? atoi(getenv("SMLA_DBG")) : 0;
-    kp.dbg_buf = reinterpret_cast<long long*>(ws + 128);   // spare bytes behind the error word
+#ifdef SMLA_TRACE
+    kp.trace = reinterpret_cast<long long*>(ws + pl.delta_off) ;   // development builds: stamps overwrite Delta[0..512)
+    kp.trace_cta = getenv("SMLA_TRACE_CTA") ? atoi(getenv("SMLA_TRACE_CTA")) : 0;
 #endif
 
     if (stages & SMLA_STAGE_DELTA) {

@@ -23,6 +23,7 @@
 
 namespace smla {
 
+constexpr unsigned kPollSleepNs = 32;   // back-off of producer / consumer warps waiting on mbarriers
 constexpr int kDQK = 576;
 constexpr int kDV = 512;
 constexpr int kQChunks = kDQK / 64;   // 9 column chunks of 64
@@ -43,11 +44,18 @@ struct KParams {
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
-#ifdef SMLA_DEBUG_KNOBS
-    int dbg;                  // experiment switches, never set in the shipped build
-    long long* dbg_buf;       // cycle counters written by CTA 0
+#ifdef SMLA_TRACE
+    long long* trace;         // development builds only: cycle stamps of CTA `trace_cta`
+    int trace_cta;
 #endif
 };
+
+#ifdef SMLA_TRACE
+// stamp event `ev` (0..7) of step `i`, steps [lo, lo+64)
+#define SMLA_STAMP(ev, i, lo) do { if (blockIdx.x == p.trace_cta && (i) >= (lo) && (i) < (lo) + 64) p.trace[((i) - (lo)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define SMLA_STAMP(ev, i, lo) do { } while (0)
+#endif
 
 // error codes recorded by bounded waits: 100*kernel + site
 enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300 };
@@ -88,309 +96,7 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 }
 
 // =============================================================================================
-// recompute: one CTA per (query, group of 64 heads), 13 warps.
-//   warps 0-3   softmax-gradient: thread = key row; reads P^T, dP^T from TMEM, writes one 128-byte
-//               row of S and of dS (bf16) to the scratch
-//   warps 4-11  gather producers: per 128-key tile nine [128 keys x 64 col] chunks of kv rows picked by
-//               index, copied with 16-byte cp.async into the 128-byte-swizzled layout the UMMA reads
-//               (the TMA gather4 path tops out near 8 B/clk per SM; 256 threads of cp.async reach ~20)
-//   warp 13     second gather path: every third chunk comes through TMA gather4 instead (4 rows per lane),
-//               which adds the TMA unit's ~8 B/clk to what the cp.async threads sustain
-//   warp 12     UMMA issuer (+ TMEM allocation, + the Q / dO chunks of the head group by TMA):
-//               P^T[128 keys, 64 heads] += Kg_chunk . Q_chunk^T  (9 chunks, K = 576)
-//               dP^T                    += Kg_chunk . dO_chunk^T (8 chunks, K = 512)
-//               accumulators double-buffered in TMEM (2 x 128 columns)
-// =============================================================================================
-namespace rc {
-constexpr int kThreads = 448;
-constexpr int kProducerWarps = 8;
-constexpr int kStages = 5;
-constexpr int kTileKeys = 128;
-constexpr int kChunkBytesA = kTileKeys * 128;  // 16 KB gathered chunk
-constexpr int kChunkBytesB = 64 * 128;         // 8 KB Q / dO chunk (64 heads)
-constexpr int kOffQ = 0;
-constexpr int kOffDO = kOffQ + kQChunks * kChunkBytesB;
-constexpr int kOffRing = kOffDO + kVChunks * kChunkBytesB;
-constexpr int kOffMisc = kOffRing + kStages * kChunkBytesA;
-constexpr int kSmemBytes = kOffMisc + 1024 + 1024;  // + misc + alignment slack
-}  // namespace rc
-
-template <int HP>
-__global__ void __launch_bounds__(rc::kThreads, 1)
-smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                      const __grid_constant__ CUtensorMap tm_kv, const KParams p) {
-    using namespace rc;
-    constexpr int G = HP / 64;
-    const int g = blockIdx.x % G;
-    const int ql = blockIdx.x / G;
-    const int qg = p.q0 + ql;
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t s_base = smem_u32(smem);
-    uint8_t* misc = smem + kOffMisc;
-    // misc: [0,512) lse2[64] + delta[64]; [512, ...) barriers; tmem ptr; abort flag
-    float* lse_s = reinterpret_cast<float*>(misc);
-    float* delta_s = lse_s + 64;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 512);
-    const uint32_t bar_full = smem_u32(bars);                  // [kStages]
-    const uint32_t bar_empty = bar_full + 8 * kStages;         // [kStages]
-    const uint32_t bar_qdo = bar_empty + 8 * kStages;          // 1
-    const uint32_t bar_tfull = bar_qdo + 8;                    // [2]
-    const uint32_t bar_tempty = bar_tfull + 16;                // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 512 + 8 * (2 * kStages + 5));
-    volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const WaitCtx wc{p.g_err, s_abort};
-
-    if (threadIdx.x == 0) {
-        *s_abort = 0;
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, kProducerWarps * 32);
-            mbar_init(bar_empty + 8 * i, 1);
-        }
-        mbar_init(bar_qdo, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 4);
-        }
-        fence_mbar_init();
-    }
-    if (warp == 12) {
-        tmem_alloc(smem_u32(tmem_slot), 256);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = *tmem_slot;
-    const int n_tiles = p.topk_pad / kTileKeys;
-
-    if (warp >= 4 && warp < 12) {
-        // ------------------------------------------------------------------ gather producers
-        const int pt = threadIdx.x - 128;   // 0..255
-        const int u = pt & 7;               // 16-byte unit inside a 128-byte chunk row
-        const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of the tile
-        const uint32_t dst0 = s_base + kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
-        const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
-        // chunks with j % 3 == 0 belong to the TMA warp
-#ifdef SMLA_DEBUG_KNOBS
-        if (!(p.dbg & 8))
-#endif
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            const char* src[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = tile * kTileKeys + r0 + 32 * i;
-                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                idx = min(max(idx, 0), p.s_kv - 1);   // unused slots gather a real row; their S, dS are forced to 0
-                src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
-            }
-            for (int j = 0; j < kQChunks; ++j) {
-                if (j % 3 == 0) continue;
-                const int it = tile * kQChunks + j;
-                const int s = it % kStages;
-                mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 1);
-                const uint32_t d = dst0 + s * kChunkBytesA;
-#ifdef SMLA_DEBUG_KNOBS
-                if (!(p.dbg & 1))
-#endif
-#pragma unroll
-                for (int i = 0; i < 4; ++i) cp_async16(d + i * 32 * 128, src[i] + j * 128);
-                cp_async_mbar_arrive_noinc(bar_full + 8 * s);   // fires when this thread's copies have landed
-            }
-        }
-    } else if (warp == 13) {
-        // ------------------------------------------------------------------ TMA gather4 path (chunks 0, 3, 6)
-        if (lane == 0) tma_prefetch_desc(&tm_kv);
-#ifdef SMLA_DEBUG_KNOBS
-        if (!(p.dbg & 8))
-#endif
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            int r[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int key = tile * kTileKeys + lane * 4 + k;
-                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                r[k] = min(max(idx, 0), p.s_kv - 1);
-            }
-            for (int j = 0; j < kQChunks; j += 3) {
-                const int it = tile * kQChunks + j;
-                const int s = it % kStages;
-                mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 6);
-                // the stage barrier counts one arrival per cp.async producer thread; stand in for all of them
-#ifdef SMLA_DEBUG_KNOBS
-                if (p.dbg & 4) {
-                    if (lane == 0) mbar_arrive_n(bar_full + 8 * s, kProducerWarps * 32);
-                    continue;
-                }
-#endif
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(bar_full + 8 * s, kChunkBytesA);
-                    mbar_arrive_n(bar_full + 8 * s, kProducerWarps * 32 - 1);
-                }
-                __syncwarp();
-                tma_gather4(s_base + kOffRing + s * kChunkBytesA + lane * 512, &tm_kv, 64 * j, r[0], r[1], r[2], r[3],
-                            bar_full + 8 * s);
-            }
-        }
-    } else if (warp == 12) {
-        // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_do);
-            mbar_arrive_expect_tx(bar_qdo, (kQChunks + kVChunks) * kChunkBytesB);
-            const int row0 = qg * p.h_q + 64 * g;
-            for (int j = 0; j < kQChunks; ++j) tma_load_2d(s_base + kOffQ + j * kChunkBytesB, &tm_q, 64 * j, row0, bar_qdo);
-            for (int j = 0; j < kVChunks; ++j) tma_load_2d(s_base + kOffDO + j * kChunkBytesB, &tm_do, 64 * j, row0, bar_qdo);
-
-            constexpr uint32_t idesc = make_idesc_bf16(128, 64, 0, 0);
-#ifdef SMLA_DEBUG_KNOBS
-            long long c_qdo = clock64(), c_tempty = 0, c_full = 0, c_issue = 0, c0;
-#endif
-            mbar_wait(bar_qdo, 0, wc, kErrRecompute + 2);
-#ifdef SMLA_DEBUG_KNOBS
-            c_qdo = clock64() - c_qdo;
-            const long long c_start = clock64();
-#endif
-            int it = 0;
-            for (int tile = 0; tile < n_tiles; ++tile) {
-                const int b = tile & 1;
-#ifdef SMLA_DEBUG_KNOBS
-                c0 = clock64();
-#endif
-                mbar_wait(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 3);
-#ifdef SMLA_DEBUG_KNOBS
-                c_tempty += clock64() - c0;
-#endif
-                tc_fence_after_sync();
-                const uint32_t d_p = tmem + b * 128;
-                const uint32_t d_dp = d_p + 64;
-                for (int j = 0; j < kQChunks; ++j, ++it) {
-                    const int s = it % kStages;
-#ifdef SMLA_DEBUG_KNOBS
-                    c0 = clock64();
-                    if (!(p.dbg & 8))
-#endif
-                    mbar_wait(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 4);
-#ifdef SMLA_DEBUG_KNOBS
-                    c_full += clock64() - c0;
-                    c0 = clock64();
-#endif
-                    fence_proxy_async_smem();   // cp.async wrote through the generic proxy, the UMMA reads through the async one
-                    tc_fence_after_sync();
-                    const uint32_t a0 = s_base + kOffRing + s * kChunkBytesA;
-                    const uint32_t bq = s_base + kOffQ + j * kChunkBytesB;
-                    const uint32_t bd = s_base + kOffDO + j * kChunkBytesB;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint64_t ad = make_smem_desc(a0 + 32 * k, 16, 1024, kSwizzle128);
-                        umma_ss(d_p, ad, make_smem_desc(bq + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
-#ifdef SMLA_DEBUG_KNOBS
-                        if (!(p.dbg & 16))
-#endif
-                        if (j < kVChunks)
-                            umma_ss(d_dp, ad, make_smem_desc(bd + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
-                    }
-                    umma_commit(bar_empty + 8 * s);
-#ifdef SMLA_DEBUG_KNOBS
-                    c_issue += clock64() - c0;
-#endif
-                }
-                umma_commit(bar_tfull + 8 * b);
-            }
-#ifdef SMLA_DEBUG_KNOBS
-            if (blockIdx.x == 0 && p.dbg_buf) {
-                p.dbg_buf[0] = c_qdo; p.dbg_buf[1] = c_tempty; p.dbg_buf[2] = c_full; p.dbg_buf[3] = c_issue;
-                p.dbg_buf[4] = clock64() - c_start;
-            }
-#endif
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax gradient
-        const int quarter = warp;
-        const int st = threadIdx.x;  // 0..127
-        if (st < 64) {
-            const int h = 64 * g + st;
-            const bool hv = h < p.h_q;
-            lse_s[st] = hv ? p.lse[static_cast<size_t>(qg) * p.h_q + h] * p.lse_mult : __int_as_float(0x7f800000);
-            delta_s[st] = hv ? p.delta[static_cast<size_t>(qg) * p.h_q + h] : 0.f;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int row = quarter * 32 + lane;
-#ifdef SMLA_DEBUG_KNOBS
-        long long s_ldg = 0, s_wait = 0, s_math = 0, s0;
-#endif
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            const int key = tile * kTileKeys + row;
-#ifdef SMLA_DEBUG_KNOBS
-            s0 = clock64();
-#endif
-            const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-            const bool valid = slot_valid(idx, qg, p);
-#ifdef SMLA_DEBUG_KNOBS
-            if (valid) s_ldg += clock64() - s0; else s_ldg += clock64() - s0 + 1;
-            s0 = clock64();
-#endif
-            const int b = tile & 1;
-            mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 5);
-#ifdef SMLA_DEBUG_KNOBS
-            s_wait += clock64() - s0;
-            s0 = clock64();
-#endif
-            tc_fence_after_sync();
-            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * 128;
-            const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + 64 * g;
-            uint4* s_out = reinterpret_cast<uint4*>(p.s_scr + off);
-            uint4* ds_out = reinterpret_cast<uint4*>(p.ds_scr + off);
-#ifdef SMLA_DEBUG_KNOBS
-            if (!(p.dbg & 2))
-#endif
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-                uint32_t pv[32], dpv[32];
-                tmem_ld_32x32(taddr + half * 32, pv);
-                tmem_ld_32x32(taddr + 64 + half * 32, dpv);
-                tmem_ld_wait();
-                uint32_t so[16], dso[16];
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    float sv[2], dsv[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int h = half * 32 + c + e;
-                        const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c + e]), p.scale_log2e, -lse_s[h])) : 0.f;
-                        sv[e] = sx;
-                        dsv[e] = valid ? sx * (__uint_as_float(dpv[c + e]) - delta_s[h]) * p.sm_scale : 0.f;
-                    }
-                    so[c >> 1] = pack_bf16x2(sv[0], sv[1]);
-                    dso[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
-                }
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    s_out[half * 4 + v] = make_uint4(so[4 * v], so[4 * v + 1], so[4 * v + 2], so[4 * v + 3]);
-                    ds_out[half * 4 + v] = make_uint4(dso[4 * v], dso[4 * v + 1], dso[4 * v + 2], dso[4 * v + 3]);
-                }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
-#ifdef SMLA_DEBUG_KNOBS
-            s_math += clock64() - s0;
-#endif
-        }
-#ifdef SMLA_DEBUG_KNOBS
-        if (blockIdx.x == 0 && threadIdx.x == 0 && p.dbg_buf) { p.dbg_buf[8] = s_ldg; p.dbg_buf[9] = s_wait; p.dbg_buf[10] = s_math; }
-#endif
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 12) tmem_dealloc(tmem, 256);
-}
-
-// =============================================================================================
-// recompute, pair version: one 2-CTA cluster per query, 18 warps per CTA.
+// recompute: one 2-CTA cluster per query, 17 warps per CTA.
 // The pair works on 256-key tiles with cta_group::2 UMMAs of shape M = 256 keys x N = 2*HP:
 //   A  each CTA gathers ITS 128 keys of the tile (every kv row is fetched once per query, not once
 //      per head group), chunk by chunk through a 5-slot ring of [128 keys x 64 col] chunks;
@@ -402,11 +108,11 @@ smla_recompute_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 //   warps 0-7   softmax-gradient on the CTA's own keys: warp w -> TMEM lane quarter w % 4, head half w / 4
 //   warps 8-15  gather producers (cp.async 16 B, swizzled); completion arrives on the slot's mbarrier
 //   warp 16     TMA of the CTA's Q / dO chunks; in the even CTA also the UMMA issuer for the pair
-//   warp 17     odd CTA only: forwards "my slot is full" to the even CTA (cp.async cannot signal remotely)
+//               in the odd CTA it forwards "my slot is full" to the even CTA (cp.async cannot signal remotely)
 // Slot-free and accumulator-ready signals are tcgen05.commit arrivals delivered to both CTAs.
 // =============================================================================================
 namespace rp {
-constexpr int kThreads = 576;
+constexpr int kThreads = 544;
 constexpr int kProducerThreads = 256;
 constexpr int kStages = 5;
 constexpr int kTileKeys = 256;             // per pair; 128 per CTA
@@ -444,22 +150,21 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     float* lse_s = reinterpret_cast<float*>(misc);          // [HP] base-2 lse, +inf for padded heads
     float* delta_s = lse_s + HP;                            // [HP]
     uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 1024);
-    const uint32_t bar_full = smem_u32(bars);               // [kStages] this CTA's gathered chunk landed
+    const uint32_t bar_full = smem_u32(bars);               // [kStages] gathered chunk landed (even CTA: in both CTAs)
     const uint32_t bar_empty = bar_full + 8 * kStages;      // [kStages] pair UMMAs reading the slot finished
-    const uint32_t bar_pfull = bar_empty + 8 * kStages;     // [kStages] (even CTA) the odd CTA's chunk landed
-    const uint32_t bar_qdo = bar_pfull + 8 * kStages;       // 1
+    const uint32_t bar_qdo = bar_empty + 8 * kStages;       // 1
     const uint32_t bar_tfull = bar_qdo + 8;                 // [2] accumulator buffer complete
     const uint32_t bar_tempty = bar_tfull + 16;             // [2] (even CTA) both CTAs have read the buffer
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (3 * kStages + 5));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 5));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const WaitCtx wc{p.g_err, s_abort};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, kProducerThreads);
+            // the even CTA's "full" also counts one arrival forwarded from the odd CTA
+            mbar_init(bar_full + 8 * i, kProducerThreads + (rank == 0 ? 1 : 0));
             mbar_init(bar_empty + 8 * i, 1);
-            mbar_init(bar_pfull + 8 * i, 1);
         }
         mbar_init(bar_qdo, 1);
         for (int i = 0; i < 2; ++i) {
@@ -505,11 +210,10 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             }
             for (int j = 0; j < kQChunks; ++j, ++it) {
                 const int s = it % kStages;
-                mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 11);
+                mbar_spin(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 11);
+                if (pt == 0) SMLA_STAMP(0, it, 18);
+                if (pt == 255) SMLA_STAMP(1, it, 18);
                 const uint32_t d = dst0 + s * kChunkA;
-#ifdef SMLA_DEBUG_KNOBS
-                if (!(p.dbg & 1))
-#endif
 #pragma unroll
                 for (int i = 0; i < 4; ++i) cp_async16_hint(d + i * 32 * 128, src[i] + j * 128, pol_keep);
                 cp_async_mbar_arrive_noinc(bar_full + 8 * s);
@@ -526,86 +230,41 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_qdo, pol_stream);
             for (int j = 0; j < kVChunks; ++j)
                 tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo, pol_stream);
-            if (rank == 0) {
+            if (rank == 1) {
+                // -------------------------------------------------------------- forward slot-full to the even CTA
+                mbar_wait(bar_qdo, 0, wc, kErrRecompute + 16, kPollSleepNs);   // Q / dO are part of what "full" promises
+                for (int it = 0; it < n_chunks; ++it) {
+                    const int s = it % kStages;
+                    mbar_spin(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 17);
+                    mbar_arrive_cluster(map_to_cta(bar_full + 8 * s, 0));
+                }
+            } else {
                 // -------------------------------------------------------------- UMMA issuer for the pair
                 constexpr uint32_t idesc = make_idesc_bf16(256, 2 * HP, 0, 0);
-#ifdef SMLA_DEBUG_KNOBS
-                long long k_wait = 0, k_fence = 0, k_issue = 0, k_commit = 0, k_tempty = 0, k_t0 = 0, k_total = 0;
-#endif
                 mbar_wait(bar_qdo, 0, wc, kErrRecompute + 12);
                 int it = 0;
                 for (int tile = 0; tile < n_tiles; ++tile) {
                     const int b = tile & 1;
-#ifdef SMLA_DEBUG_KNOBS
-                    long long c1 = clock64();
-#endif
-                    mbar_wait(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
-#ifdef SMLA_DEBUG_KNOBS
-                    k_tempty += clock64() - c1; if (tile == 0) k_t0 = clock64(); if (tile == n_tiles - 1) k_total = clock64() - k_t0;
-#endif
+                    mbar_spin(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
                     tc_fence_after_sync();
                     const uint32_t d = tmem + b * C::kAccCols;
                     for (int j = 0; j < kQChunks; ++j, ++it) {
                         const int s = it % kStages;
-                        const uint32_t ph = (it / kStages) & 1;
-#ifdef SMLA_DEBUG_KNOBS
-                        long long c0 = clock64();
-                        if (!(p.dbg & 8)) {
-#endif
-                        mbar_wait(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
-                        mbar_wait(bar_pfull + 8 * s, ph, wc, kErrRecompute + 15);
-#ifdef SMLA_DEBUG_KNOBS
-                        }
-                        k_wait += clock64() - c0;
-                        c0 = clock64();
-                        if (!(p.dbg & 32))
-#endif
-                        fence_proxy_async_smem();   // cp.async wrote through the generic proxy
-                        tc_fence_after_sync();
-#ifdef SMLA_DEBUG_KNOBS
-                        k_fence += clock64() - c0;
-                        c0 = clock64();
-#endif
-                        const uint32_t a0 = s_base + C::kOffRing + s * kChunkA;
-                        const uint32_t b0 = s_base + C::kOffB + j * C::kBChunk;
+                        SMLA_STAMP(2, it, 18);
+                        mbar_spin(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 14);
+                        SMLA_STAMP(3, it, 18);
+                        const uint64_t ad = make_smem_desc(s_base + C::kOffRing + s * kChunkA, 16, 1024, kSwizzle128);
+                        const uint64_t bd = make_smem_desc(s_base + C::kOffB + j * C::kBChunk, 16, 1024, kSwizzle128);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma_ss_2cta(d, make_smem_desc(a0 + 32 * k, 16, 1024, kSwizzle128),
-                                         make_smem_desc(b0 + 32 * k, 16, 1024, kSwizzle128), idesc, (j | k) != 0);
-#ifdef SMLA_DEBUG_KNOBS
-                        k_issue += clock64() - c0;
-                        c0 = clock64();
-#endif
-                        umma_commit_2cta(bar_empty + 8 * s);
-                        umma_commit_2cta(map_to_cta(bar_empty + 8 * s, 1));
-#ifdef SMLA_DEBUG_KNOBS
-                        k_commit += clock64() - c0;
-#endif
+                        for (int k = 0; k < 4; ++k)   // 32 bytes further along K = +2 in the descriptor's address field
+                            umma_ss_2cta(d, ad + 2 * k, bd + 2 * k, idesc, (j | k) != 0);
+                        SMLA_STAMP(4, it, 18);
+                        umma_commit_2cta_mask(bar_empty + 8 * s, 3);
+                        SMLA_STAMP(5, it, 18);
                     }
-                    umma_commit_2cta(bar_tfull + 8 * b);
-                    umma_commit_2cta(map_to_cta(bar_tfull + 8 * b, 1));
+                    umma_commit_2cta_mask(bar_tfull + 8 * b, 3);
                 }
-#ifdef SMLA_DEBUG_KNOBS
-                if (blockIdx.x == 0) {
-                    p.dbg_buf[0] = k_wait; p.dbg_buf[1] = k_fence; p.dbg_buf[2] = k_tempty; p.dbg_buf[5] = k_issue;
-                    p.dbg_buf[6] = k_commit; p.dbg_buf[4] = k_total;
-                }
-#endif
             }
-        }
-    } else if (warp == 17) {
-        if (lane == 0 && rank == 1) {
-            // ---------------------------------------------------------------- forward slot-full to the even CTA
-            mbar_wait(bar_qdo, 0, wc, kErrRecompute + 16);   // Q / dO of this CTA are part of what "full" promises
-            for (int it = 0; it < n_chunks; ++it) {
-                const int s = it % kStages;
-                mbar_wait(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 17);
-                fence_proxy_async_smem();
-                mbar_arrive_cluster(map_to_cta(bar_pfull + 8 * s, 0));
-            }
-        } else if (lane == 0) {
-            // the even CTA's own chunks need no forwarding; complete its pfull phases locally? no: pfull counts
-            // only the odd CTA's arrival, nothing to do here
         }
     } else {
         // ------------------------------------------------------------------ softmax gradient (own 128 keys)
@@ -625,15 +284,13 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
             const bool valid = slot_valid(idx, qg, p);
             const int b = tile & 1;
-            mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 18);
+            mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
+            if (threadIdx.x == 0) SMLA_STAMP(6, tile * kQChunks, 18);
             tc_fence_after_sync();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
             const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
             __nv_bfloat16* s_out = p.s_scr + off;
             __nv_bfloat16* ds_out = p.ds_scr + off;
-#ifdef SMLA_DEBUG_KNOBS
-            if (!(p.dbg & 2))
-#endif
 #pragma unroll 1
             for (int c0 = 0; c0 < NH; c0 += 16) {
                 uint32_t pv[16], dpv[16];
@@ -660,6 +317,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
+            if (threadIdx.x == 0) SMLA_STAMP(7, tile * kQChunks, 18);
         }
     }
     tc_fence_before_sync();
@@ -772,7 +430,7 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int j = 0; j < n_do; ++j)
                 tma_load_2d_hint(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res, pol_stream);
             for (int tile = 0; tile < n_tiles; ++tile) {
-                mbar_wait(bar_sempty, (tile & 1) ^ 1, wc, kErrDkv + 1);
+                mbar_wait(bar_sempty, (tile & 1) ^ 1, wc, kErrDkv + 1, kPollSleepNs);
                 mbar_arrive_expect_tx(bar_sfull, C::kStage);
                 const int row = ql * p.topk_pad + tile * kTileKeys;
                 const uint32_t dst = s_base + C::kOffStage;
@@ -830,7 +488,7 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             __syncwarp();
             for (int blk = 0; blk < n_blk; ++blk, ++unit) {
                 const int us = unit % kUnits;
-                mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5);
+                mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
                 tc_fence_after_sync();
                 if (!(part == 0 && blk == 2 && quarter >= 2)) {   // padded rows are never drained
                     float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane;
@@ -948,7 +606,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                 idx = min(max(idx, 0), p.s_kv - 1);
                 src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
             }
-            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1);
+            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);
             const uint32_t d = dst0 + s * C::kStage;
             for (int c = kTmaChunks; c < n_ch; ++c) {
                 cp_async16_hint(d + c * 8192, src[0] + c * 128, pol_keep);
@@ -973,7 +631,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                     r[k] = min(max(idx, 0), p.s_kv - 1);
                 }
             }
-            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4);
+            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4, kPollSleepNs);
             const uint32_t dst = s_base + s * C::kStage;
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
@@ -1010,7 +668,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         }
     } else {
         const int quarter = warp;
-        mbar_wait(bar_acc, 0, wc, kErrDq + 3);
+        mbar_wait(bar_acc, 0, wc, kErrDq + 3, kPollSleepNs);
         tc_fence_after_sync();
         for (int blk = 0; blk < n_blk; ++blk) {
             if (part == 0 && blk == 2 && quarter >= 2) continue;
