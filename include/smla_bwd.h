@@ -31,6 +31,7 @@ extern "C" {
 #define SMLA_ERR_LAUNCH 2         /* a CUDA runtime or driver call failed (reference prints and ignores, mla_bwd.cu:814-818,965-968) */
 #define SMLA_ERR_WORKSPACE 3      /* workspace too small */
 #define SMLA_ERR_DEVICE_TIMEOUT 4 /* a bounded wait inside a kernel ran out; results are invalid */
+#define SMLA_ERR_TOO_LARGE_FOR_STATIC 5 /* smla_bwd_run_noalloc: does not fit the built-in workspace */
 
 /* stages of smla_bwd_run_stages (bit mask) */
 #define SMLA_STAGE_ZERO 1      /* clear dKV                           (reference: torch::zeros, mla_bwd.cu:1027) */
@@ -69,6 +70,33 @@ int smla_bwd_run(const smla_bwd_params* p, void* workspace, size_t workspace_byt
  * dKV over several calls) and lets tests and profilers run one kernel at a time. */
 int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream,
                         int stage_mask);
+
+/* Whole backward for callers that must not allocate device memory.  (No counterpart in the reference, whose
+ * operator allocates delta, dQ and dKV itself on every call.)
+ *
+ * Who needs it: host code that runs where a cudaMalloc is off limits -- a plugin inside a process whose
+ * framework has already reserved the GPU's memory for its own pool (a raw allocation there fails or
+ * fragments the pool), or a latency-bound loop that cannot take the device-wide synchronisation an
+ * allocation or free may imply.  Such a caller still owns q, kv, dO, lse, O, indices, dQ and dKV; what it cannot
+ * provide is the scratch for Delta and the bf16 S / dS.  This entry point takes that scratch from a
+ * 32 MiB array compiled into the library (smla_bwd_noalloc_capacity()), resident on every GPU that loads
+ * the library until the process exits.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Limits and rules:
+ *  - 256 + 4*s_q*h_q bytes of Delta plus the S/dS of at least one query (4 * topk_pad * h_pad bytes, topk
+ *    rounded up to 256, heads to 64 or 128) must fit in the 32 MiB; otherwise SMLA_ERR_TOO_LARGE_FOR_STATIC.
+ *    Larger s_q simply takes more passes over the query dimension (about 31 queries per pass at
+ *    h_q 128 / topk 2048), so this path trades speed for not allocating.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ *    device current) and caches it; make that first call before any stream capture begins.
+ *  - All calls on a device share the one array.  It keeps whatever the previous call left; every byte that
+ *    is read is rewritten first (the error word is cleared, Delta and the S/dS rows of a pass are fully
+ *    overwritten before use).  Two calls whose kernels overlap on the GPU (different streams, or threads)
+ *    race on it: serialise them.
+ *  - Status of the last call: smla_bwd_noalloc_status(stream) (synchronises the stream). */
+int smla_bwd_run_noalloc(const smla_bwd_params* p, void* stream);
+size_t smla_bwd_noalloc_capacity(void);
+int smla_bwd_noalloc_status(void* stream);
 
 /* Delta only: delta[s_q, h_q] = sum_j O[.., j] * dO[.., j]   (reference: launch_preprocess_delta). */
 int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int32_t h_q, void* stream);

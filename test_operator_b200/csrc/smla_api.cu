@@ -197,6 +197,30 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ---- workspace that lives in the library image (smla_bwd_run_noalloc) -----------------------------------
+// Every GPU that loads the library carries these bytes until the process exits.
+constexpr size_t kStaticWorkspaceBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_ws_mutex;
+void* g_static_ws_ptr[kMaxDevices] = {};   // device address of g_static_workspace, per device ordinal
+
+// The array's name is only a host-side handle; the kernels need its device address, which is looked up
+// once per device (with that device current) and cached.
+int static_workspace_ptr(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SMLA_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+    if (!g_static_ws_ptr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || !ptr) return SMLA_ERR_LAUNCH;
+        g_static_ws_ptr[dev] = ptr;
+    }
+    *out = g_static_ws_ptr[dev];
+    return SMLA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -246,6 +270,27 @@ int smla_bwd_run(const smla_bwd_params* p, void* workspace, size_t workspace_byt
     return smla_bwd_run_stages(p, workspace, workspace_bytes, stream, SMLA_STAGE_ALL);
 }
 
+int smla_bwd_run_noalloc(const smla_bwd_params* p, void* stream) {
+    g_last_launches = 0;
+    Plan pl;
+    if (!check_params(p)) return SMLA_ERR_BAD_ARG;
+    // the fixed part (error word, Delta) plus the S / dS scratch of at least one query must fit the built-in array
+    if (!plan_for_workspace(p, kStaticWorkspaceBytes, &pl)) return SMLA_ERR_TOO_LARGE_FOR_STATIC;
+    void* ws = nullptr;
+    const int st = static_workspace_ptr(&ws);
+    if (st != SMLA_OK) return st;
+    return smla_bwd_run_stages(p, ws, kStaticWorkspaceBytes, stream, SMLA_STAGE_ALL);
+}
+
+size_t smla_bwd_noalloc_capacity(void) { return kStaticWorkspaceBytes; }
+
+int smla_bwd_noalloc_status(void* stream) {
+    void* ws = nullptr;
+    const int st = static_workspace_ptr(&ws);
+    if (st != SMLA_OK) return st;
+    return smla_bwd_status(ws, stream);
+}
+
 int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int32_t h_q, void* stream) {
     if (!O || !dO || !delta || s_q <= 0 || h_q <= 0 || !aligned16(O) || !aligned16(dO)) return SMLA_ERR_BAD_ARG;
     if (static_cast<long long>(s_q) * h_q > INT_MAX) return SMLA_ERR_BAD_ARG;
@@ -274,6 +319,9 @@ const char* smla_status_string(int status) {
         case SMLA_ERR_LAUNCH: return "CUDA launch or driver call failed";
         case SMLA_ERR_WORKSPACE: return "workspace too small";
         case SMLA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out; results are invalid";
+        case SMLA_ERR_TOO_LARGE_FOR_STATIC:
+            return "problem too large for the library's built-in 32 MiB workspace (Delta + one query of S/dS must fit); "
+                   "use smla_bwd_run with a caller-provided workspace";
         default: return "unknown status";
     }
 }

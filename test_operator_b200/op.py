@@ -77,6 +77,11 @@ def load_library() -> ctypes.CDLL:
                                                       ctypes.POINTER(WorkspaceLayout)]
         lib.smla_bwd_status.restype = ctypes.c_int
         lib.smla_bwd_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.smla_bwd_run_noalloc.restype = ctypes.c_int
+        lib.smla_bwd_run_noalloc.argtypes = [ctypes.POINTER(_Params), ctypes.c_void_p]
+        lib.smla_bwd_noalloc_capacity.restype = ctypes.c_size_t
+        lib.smla_bwd_noalloc_status.restype = ctypes.c_int
+        lib.smla_bwd_noalloc_status.argtypes = [ctypes.c_void_p]
         lib.smla_bwd_last_launch_count.restype = ctypes.c_int
         lib.smla_bwd_status_string = lib.smla_status_string
         lib.smla_status_string.restype = ctypes.c_char_p
@@ -195,6 +200,21 @@ def mla_bwd(
         if check_device_status:
             _raise_status(lib, lib.smla_bwd_status(workspace.ptr, stream), "smla_bwd device status")
     return dQ, dKV
+
+
+def mla_bwd_noalloc(q, kv, dO, lse, O, indices, dQ, dKV, sm_scale: Optional[float] = None,
+                    q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True) -> None:
+    """Backward into caller-owned `dQ` / `dKV` using the library's built-in scratch: nothing is allocated,
+    neither here nor in the library.  For callers that must not touch the device allocator (see
+    `smla_bwd_run_noalloc` in include/smla_bwd.h for who they are and for the size limit).  Calls on one device
+    must not overlap: they share the scratch."""
+    _validate(q, kv, dO, lse, O, indices)
+    lib = load_library()
+    params = _make_params(q, kv.view(kv.shape[0], D_QK), dO, lse, O, indices.view(indices.shape[0], indices.shape[-1]),
+                          dQ, dKV, sm_scale, q_start_index_s, lse_is_base2)
+    with torch.cuda.device(q.device):
+        st = lib.smla_bwd_run_noalloc(ctypes.byref(params), torch.cuda.current_stream().cuda_stream)
+    _raise_status(lib, st, "smla_bwd_run_noalloc")
 
 
 def run_stages(q, kv, dO, lse, O, indices, dQ, dKV, workspace: Workspace, stages: int, sm_scale=None,
