@@ -271,20 +271,55 @@ def last_launch_count() -> int:
 def mla_bwd_host(q, kv, dO, lse, O, indices, device, sm_scale: Optional[float] = None,
                  q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True,
                  workspace: Optional[Workspace] = None, out_dq: Optional[torch.Tensor] = None,
-                 out_dkv: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Same operator for HOST tensors: copies the inputs to `device`, runs the backward there and
-    returns (dQ, dKV) as host tensors (written into `out_dq` / `out_dkv` when given; pinned buffers
-    make the copies asynchronous).  Synchronises before returning."""
+                 out_dkv: Optional[torch.Tensor] = None, n_chunks: int = 8) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same operator for HOST tensors (pinned memory makes the copies asynchronous).
+
+    The query dimension is cut into `n_chunks` blocks and pipelined over three streams: block i+1 is
+    copied to `device` while block i runs and the dQ of block i-1 travels back; every block adds into
+    one fp32 dKV on the device, which returns last.  Returns (dQ, dKV) as host tensors (written into
+    `out_dq` / `out_dkv` when given) and synchronises before returning.
+    """
     dev = torch.device(device)
+    s_q = q.shape[0]
+    n_chunks = max(1, min(n_chunks, s_q))
+    bounds = [(i * s_q) // n_chunks for i in range(n_chunks + 1)]
+    if out_dq is None:
+        out_dq = torch.empty(q.shape, dtype=torch.bfloat16, pin_memory=True)
+    if out_dkv is None:
+        out_dkv = torch.empty(kv.shape, dtype=torch.float32, pin_memory=True)
     with torch.cuda.device(dev):
-        d = [t.to(dev, non_blocking=True) for t in (q, kv, dO, lse, O, indices)]
-        dq, dkv = mla_bwd(*d, sm_scale=sm_scale, q_start_index_s=q_start_index_s, lse_is_base2=lse_is_base2,
-                          workspace=workspace)
-        if out_dq is None:
-            out_dq = torch.empty(dq.shape, dtype=dq.dtype, pin_memory=True)
-        if out_dkv is None:
-            out_dkv = torch.empty(dkv.shape, dtype=dkv.dtype, pin_memory=True)
-        out_dq.copy_(dq, non_blocking=True)
-        out_dkv.copy_(dkv, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        s_comp = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        s_in.wait_stream(s_comp)
+        with torch.cuda.stream(s_in):
+            kv_d = kv.to(dev, non_blocking=True)
+        dkv_d = torch.zeros(kv.shape, dtype=torch.float32, device=dev)
+        keep = []
+        for c in range(n_chunks):
+            r0, r1 = bounds[c], bounds[c + 1]
+            if r1 == r0:
+                continue
+            with torch.cuda.stream(s_in):
+                blk = [t[r0:r1].to(dev, non_blocking=True) for t in (q, dO, lse, O, indices)]
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            s_comp.wait_event(ev_in)
+            for t in blk + [kv_d]:
+                t.record_stream(s_comp)
+            qs = None if q_start_index_s is None else q_start_index_s + r0
+            dq_d, _ = mla_bwd(blk[0], kv_d, blk[1], blk[2], blk[3], blk[4], sm_scale=sm_scale, q_start_index_s=qs,
+                              lse_is_base2=lse_is_base2, out_dkv=dkv_d, accumulate=True, workspace=workspace)
+            ev_c = torch.cuda.Event()
+            ev_c.record(s_comp)
+            s_out.wait_event(ev_c)
+            with torch.cuda.stream(s_out):
+                out_dq[r0:r1].copy_(dq_d, non_blocking=True)
+            dq_d.record_stream(s_out)
+            keep.append((blk, dq_d))
+        s_out.wait_stream(s_comp)
+        with torch.cuda.stream(s_out):
+            out_dkv.copy_(dkv_d, non_blocking=True)
+        dkv_d.record_stream(s_out)
+        s_out.synchronize()
+        s_comp.synchronize()
     return out_dq, out_dkv
