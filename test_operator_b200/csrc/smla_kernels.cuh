@@ -298,18 +298,24 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 tmem_ld_32x16(taddr + NH + c0, dpv);
                 tmem_ld_wait();
                 uint32_t so[8], dso[8];
+                const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
+                const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
 #pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    float sv[2], dsv[2];
+                for (int v = 0; v < 4; ++v) {
+                    const float4 l = l4[v], dl = d4[v];
+                    const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {dl.x, dl.y, dl.z, dl.w};
+                    float sv[4], dsv[4];
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int h = g * NH + c0 + c + e;
-                        const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c + e]), p.scale_log2e, -lse_s[h])) : 0.f;
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * v + e;
+                        const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e])) : 0.f;
                         sv[e] = sx;
-                        dsv[e] = valid ? sx * (__uint_as_float(dpv[c + e]) - delta_s[h]) * p.sm_scale : 0.f;
+                        dsv[e] = valid ? sx * (__uint_as_float(dpv[c]) - dv[e]) * p.sm_scale : 0.f;
                     }
-                    so[c >> 1] = pack_bf16x2(sv[0], sv[1]);
-                    dso[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+                    so[2 * v] = pack_bf16x2(sv[0], sv[1]);
+                    so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]);
+                    dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
+                    dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
                 }
                 st_global_v8_hint(s_out + c0, so, pol_stream);
                 st_global_v8_hint(ds_out + c0, dso, pol_stream);
