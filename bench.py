@@ -33,6 +33,10 @@ from test_operator_b200.inputs import WORKLOADS, make_sequence  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 STAGE_NAMES = {2: "delta", 4: "recompute", 8: "dkv", 16: "dq"}
+# DRAM bytes (read + write) per query of each kernel at h_q 128 / top-k 2048, from the ncu captures summarised in
+# profiles/ (296-query case, dram__bytes_read.sum + dram__bytes_write.sum divided by 296; every kernel's DRAM
+# traffic grows in proportion to the number of queries).  None: no capture for that shape.
+DRAM_BYTES_PER_QUERY_H128_TOPK2048 = {"recompute": 1.352e6, "dkv": 2.673e6, "dq": 0.727e6}
 # share of the 5504 FLOPs per slot each kernel carries: recompute = P + dP, dkv = dV + dK, dq = dQ
 STAGE_FLOP_SHARE = {4: (2 * 576 + 2 * 512) / 5504.0, 8: (2 * 512 + 2 * 576) / 5504.0, 16: 2 * 576 / 5504.0}
 
@@ -47,13 +51,20 @@ def load_peaks():
 
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples of one GPU while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.proc = None
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
@@ -72,20 +83,31 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
+        import datetime
         sm, smax, reasons = [], [], set()
+        all_sm, all_max = [], []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, cmax = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for n, v in zip(names, parts[3:7]):
+            all_sm.append(clk)
+            all_max.append(cmax)
+            # samples taken while the timed steps ran (the sampler starts earlier so that it is up to speed)
+            if self.t0 is not None and self.t1 is not None and not (self.t0 - 0.05 <= ts <= self.t1 + 0.05):
+                continue
+            sm.append(clk)
+            smax.append(cmax)
+            for n, v in zip(names, parts[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
+        if not sm:          # timed region shorter than the sampling period: fall back to every sample taken
+            sm, smax = all_sm, all_max
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
 
@@ -206,19 +228,21 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
     launches[0] = 0
-    sampler = ClockSampler(local)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_begin()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -265,6 +289,10 @@ def run_ours(args):
         roofline = {"bound": "tensor", "kernel": f"smla_{dom}_kernel", "achieved": mm[dom]["tflops"], "peak": peak,
                     "unit": "TFLOP/s", "frac": mm[dom]["tflops"] / peak, "peak_kind": peak_kind + " burst",
                     "traffic": None}
+        per_q = DRAM_BYTES_PER_QUERY_H128_TOPK2048.get(dom)
+        if per_q is not None and w.h_q == 128 and w.topk == 2048:
+            roofline["traffic"] = per_q * seqs[0]["q"].shape[0]
+            roofline["traffic_note"] = "DRAM bytes per launch, scaled from the 296-query ncu capture in profiles/"
 
     # ---- end to end from pinned host buffers --------------------------------------------------------------
     e2e = None
@@ -305,8 +333,8 @@ def run_ours(args):
     if rank == 0 and world == 1 and seqs and not args.no_cpu:
         threads = os.cpu_count() or 1
         _, dt = _oracle_tflops(seqs[0], w, 8, threads)          # calibrate
-        n = int(max(16, min(seqs[0]["q"].shape[0], 15.0 / max(dt / 8, 1e-4))))
-        n = min(n, 2048)
+        _, dt = _oracle_tflops(seqs[0], w, 32, threads)         # second, warmed-up calibration
+        n = int(max(16, min(seqs[0]["q"].shape[0], 15.0 / max(dt / 32, 1e-4))))
         val, dt = _oracle_tflops(seqs[0], w, n, threads)
         cpu_baseline = {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                         "sample": f"first {n} of {seqs[0]['q'].shape[0]} queries of sequence 0, full kv and top-k, {dt:.1f} s"}
