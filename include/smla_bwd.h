@@ -98,6 +98,24 @@ int smla_bwd_run_noalloc(const smla_bwd_params* p, void* stream);
 size_t smla_bwd_noalloc_capacity(void);
 int smla_bwd_noalloc_status(void* stream);
 
+/* ---- forward (the step before this path) ---------------------------------------------------------------
+ * o = softmax(scale * q K_g^T) V_g and the log-sum-exp the backward consumes, for the same top-k indices.
+ * The reference has no forward kernel; its tests build o / lse with fp32 torch code
+ * (dq_test/test_dq_phase.py:53-59), which is what this entry point reproduces on the GPU. */
+typedef struct smla_fwd_params {
+    const void* q;          /* bf16 [s_q, h_q, 576] */
+    const void* kv;         /* bf16 [s_kv, 576] */
+    const int32_t* indices; /* i32  [s_q, topk] */
+    void* o;                /* bf16 [s_q, h_q, 512], fully overwritten (0 for a query without a valid slot) */
+    float* lse;             /* f32  [s_q, h_q] (+inf for a query without a valid slot) */
+    int32_t s_q, s_kv, h_q, topk;
+    float sm_scale;          /* <= 0 selects 1/sqrt(576) */
+    int32_t q_start_index_s; /* as in smla_bwd_params */
+    int32_t lse_is_base2;    /* 1: write lse in base-2 units (what smla_bwd_run expects by default); 0: natural log */
+} smla_fwd_params;
+size_t smla_fwd_workspace_size(const smla_fwd_params* p, size_t budget_bytes);
+int smla_fwd_run(const smla_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Delta only: delta[s_q, h_q] = sum_j O[.., j] * dO[.., j]   (reference: launch_preprocess_delta). */
 int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int32_t h_q, void* stream);
 

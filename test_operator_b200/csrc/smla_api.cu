@@ -140,7 +140,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     if (!ok) return SMLA_ERR_LAUNCH;
 
     // per device, so set on every call (cheap) rather than once per process
-    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP>, rp::Cfg<HP>::kSmemBytes);
+    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, false>, rp::Cfg<HP, false>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_kernel<HP>, dk::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dq_kernel<HP>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
@@ -154,6 +154,10 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     kp.ds_scr = ds_scr;
     kp.dKV = p->dKV;
     kp.dQ = reinterpret_cast<__nv_bfloat16*>(p->dQ);
+    kp.gout = kp.dQ;
+    kp.gout_pitch = kDQK;
+    kp.g_split = kSplitChunk;
+    kp.g_total = kQChunks;
     kp.g_err = reinterpret_cast<int*>(ws + pl.err_off);
     kp.s_q = p->s_q;
     kp.s_kv = p->s_kv;
@@ -180,7 +184,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         if (stages & SMLA_STAGE_RECOMPUTE) {
-            smla_recompute_pair_kernel<HP><<<nq * 2, rp::kThreads, rp::Cfg<HP>::kSmemBytes, st>>>(tm_qnh, tm_donh, kp);
+            smla_recompute_pair_kernel<HP, false><<<nq * 2, rp::kThreads, rp::Cfg<HP, false>::kSmemBytes, st>>>(tm_qnh, tm_donh, kp);
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DKV) {
@@ -196,6 +200,102 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---- forward ---------------------------------------------------------------------------------------------
+struct FwdPlan {
+    int h_pad, topk_pad, q_chunk;
+    size_t err_off, logits_off, s_off, total;
+};
+
+bool check_fwd_params(const smla_fwd_params* p) {
+    if (!p) return false;
+    if (p->s_q <= 0 || p->s_kv <= 0 || p->topk <= 0) return false;
+    if (p->h_q <= 0 || p->h_q > 128 || (p->h_q % 8) != 0) return false;
+    if (static_cast<long long>(p->s_q) * p->h_q > INT_MAX) return false;
+    return true;
+}
+
+bool make_fwd_plan(const smla_fwd_params* p, size_t budget, FwdPlan* pl) {
+    if (!check_fwd_params(p)) return false;
+    pl->h_pad = p->h_q <= 64 ? 64 : 128;
+    pl->topk_pad = (p->topk + 255) / 256 * 256;
+    const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;   // one bf16 matrix per query
+    const size_t per_q = 3 * unit;                              // fp32 logits + bf16 S
+    if (budget == 0) budget = kDefaultBudget;
+    size_t qc = budget > kAlign ? (budget - kAlign) / per_q : 0;
+    if (qc < 1) qc = 1;
+    if (qc > size_t(p->s_q)) qc = p->s_q;
+    while (qc > 1 && qc * size_t(pl->topk_pad) > size_t(INT_MAX)) qc /= 2;
+    pl->q_chunk = int(qc);
+    pl->err_off = 0;
+    pl->logits_off = kAlign;
+    pl->s_off = align_up(pl->logits_off + qc * 2 * unit, kAlign);
+    pl->total = align_up(pl->s_off + qc * unit, kAlign);
+    return true;
+}
+
+bool fwd_plan_for_workspace(const smla_fwd_params* p, size_t ws_bytes, FwdPlan* pl) {
+    if (!make_fwd_plan(p, ws_bytes, pl)) return false;
+    while (pl->total > ws_bytes && pl->q_chunk > 1) {
+        const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;
+        const size_t over = pl->total - ws_bytes;
+        int dec = int(over / (3 * unit)) + 1;
+        const int qc = pl->q_chunk - dec < 1 ? 1 : pl->q_chunk - dec;
+        pl->q_chunk = qc;
+        pl->s_off = align_up(pl->logits_off + size_t(qc) * 2 * unit, kAlign);
+        pl->total = align_up(pl->s_off + size_t(qc) * unit, kAlign);
+    }
+    return pl->total <= ws_bytes;
+}
+
+template <int HP>
+int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, cudaStream_t st) {
+    using namespace smla;
+    float* logits = reinterpret_cast<float*>(ws + pl.logits_off);
+    __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
+    CUtensorMap tm_qnh, tm_kv, tm_s;
+    const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
+    const uint64_t srows = uint64_t(pl.q_chunk) * pl.topk_pad;
+    bool ok = true;
+    ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
+    ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
+    ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
+    if (!ok) return SMLA_ERR_LAUNCH;
+    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, true>, rp::Cfg<HP, true>::kSmemBytes);
+    attr_ok &= set_smem(smla_dq_kernel<HP>, dq::Cfg<HP>::kSmemBytes);
+    if (!attr_ok) return SMLA_ERR_LAUNCH;
+
+    KParams kp{};
+    kp.kv = reinterpret_cast<const __nv_bfloat16*>(p->kv);
+    kp.indices = p->indices;
+    kp.s_scr = s_scr;
+    kp.logits = logits;
+    kp.lse_out = p->lse;
+    kp.lse_out_mult = p->lse_is_base2 ? 1.0f : 0.6931471805599453f;
+    kp.g_err = reinterpret_cast<int*>(ws + pl.err_off);
+    kp.s_q = p->s_q;
+    kp.s_kv = p->s_kv;
+    kp.h_q = p->h_q;
+    kp.topk = p->topk;
+    kp.topk_pad = pl.topk_pad;
+    kp.sm_scale = p->sm_scale > 0.f ? p->sm_scale : 1.0f / sqrtf(float(kDQK));
+    kp.scale_log2e = kp.sm_scale * 1.4426950408889634f;
+    kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
+    kp.q_start = kp.causal ? p->q_start_index_s : 0;
+    kp.gout = reinterpret_cast<__nv_bfloat16*>(p->o);
+    kp.gout_pitch = kDV;
+    kp.g_split = kVChunks / 2;    // o = S.V: the two d-parts gather V column chunks [0,4) and [4,8)
+    kp.g_total = kVChunks;
+    for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
+        const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
+        kp.q0 = q0;
+        smla_recompute_pair_kernel<HP, true><<<nq * 2, rp::kThreads, rp::Cfg<HP, true>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
+        smla_fwd_softmax_kernel<HP><<<nq, 512, 0, st>>>(kp);
+        smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_s, kp);
+        g_last_launches += 3;
+    }
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
 
 // ---- workspace that lives in the library image (smla_bwd_run_noalloc) -----------------------------------
 // Every GPU that loads the library carries these bytes until the process exits.
@@ -289,6 +389,26 @@ int smla_bwd_noalloc_status(void* stream) {
     const int st = static_workspace_ptr(&ws);
     if (st != SMLA_OK) return st;
     return smla_bwd_status(ws, stream);
+}
+
+size_t smla_fwd_workspace_size(const smla_fwd_params* p, size_t budget_bytes) {
+    FwdPlan pl;
+    if (!make_fwd_plan(p, budget_bytes, &pl)) return 0;
+    return pl.total;
+}
+
+int smla_fwd_run(const smla_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+    g_last_launches = 0;
+    if (!check_fwd_params(p) || !workspace) return SMLA_ERR_BAD_ARG;
+    if (!p->q || !p->kv || !p->indices || !p->o || !p->lse) return SMLA_ERR_BAD_ARG;
+    if (!aligned16(p->q) || !aligned16(p->kv) || !aligned16(p->o) || (reinterpret_cast<uintptr_t>(workspace) & (kAlign - 1)))
+        return SMLA_ERR_BAD_ARG;
+    FwdPlan pl;
+    if (!fwd_plan_for_workspace(p, workspace_bytes, &pl)) return SMLA_ERR_WORKSPACE;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    if (cudaMemsetAsync(ws + pl.err_off, 0, 4, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
+    return pl.h_pad == 64 ? launch_fwd_chain<64>(p, pl, ws, st) : launch_fwd_chain<128>(p, pl, ws, st);
 }
 
 int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int32_t h_q, void* stream) {

@@ -39,6 +39,13 @@ struct KParams {
     __nv_bfloat16* ds_scr;    // [q_chunk, topk_pad, HP]
     float* dKV;               // [s_kv, 576]
     __nv_bfloat16* dQ;        // [s_q, h_q, 576]
+    // forward only
+    float* logits;            // [q_chunk, topk_pad, HP] base-2 logits, -inf where masked
+    float* lse_out;           // [s_q, h_q]
+    float lse_out_mult;       // 1 (base 2) or ln 2 (natural log)
+    // dq-style kernel: which column chunks of kv the two d-parts gather, and where the result goes
+    __nv_bfloat16* gout;      // [s_q, h_q, gout_pitch]
+    int gout_pitch, g_split, g_total;
     int* g_err;
     int q0;                   // first query (global row) of this pass
     int s_q, s_kv, h_q, topk, topk_pad;
@@ -114,29 +121,33 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 namespace rp {
 constexpr int kThreads = 544;
 constexpr int kProducerThreads = 256;
-constexpr int kStages = 5;
 constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;         // 16 KB gathered chunk
-template <int HP> struct Cfg {
+// kFwd = false: backward recompute (B = [Q | dO], outputs bf16 S and dS)
+// kFwd = true : forward logits     (B = Q only, outputs fp32 base-2 logits); the shared memory dO would
+//               take goes to a deeper gather ring
+template <int HP, bool kFwd> struct Cfg {
     static constexpr int NH = HP / 2;                  // heads whose Q / dO rows this CTA holds
+    static constexpr int kStages = kFwd ? 9 : 5;
     static constexpr int kBHalf = NH * 128;            // one [NH heads x 64 col] chunk
-    static constexpr int kBChunk = 2 * kBHalf;         // stacked [Q_j | dO_j]
+    static constexpr int kBChunk = kFwd ? kBHalf : 2 * kBHalf;   // Q_j alone, or stacked [Q_j | dO_j]
     static constexpr int kOffB = 0;
     static constexpr int kOffRing = kQChunks * kBChunk;
     static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
     static constexpr int kSmemBytes = kOffMisc + 1024 + 256 + 1024;   // lse/delta + barriers + alignment slack
-    static constexpr int kAccCols = 2 * HP;            // one accumulator buffer
-    static constexpr int kTmemCols = 4 * HP;           // two buffers: 512 (HP 128) or 256 (HP 64)
+    static constexpr int kAccCols = kFwd ? HP : 2 * HP;            // one accumulator buffer
+    static constexpr int kTmemCols = 2 * kAccCols;                 // two buffers
 };
 }  // namespace rp
 
-template <int HP>
+template <int HP, bool kFwd>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(rp::kThreads, 1)
 smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                            const KParams p) {
     using namespace rp;
-    using C = Cfg<HP>;
+    using C = Cfg<HP, kFwd>;
     constexpr int NH = C::NH;
+    constexpr int kStages = C::kStages;
     const uint32_t rank = cluster_ctarank();
     const int ql = blockIdx.x >> 1;
     const int qg = p.q0 + ql;
@@ -173,7 +184,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         }
         fence_mbar_init();
     }
-    {   // zero block standing in for the dO half of column chunk 8
+    if constexpr (!kFwd) {   // zero block standing in for the dO half of column chunk 8
         uint4* z = reinterpret_cast<uint4*>(smem + C::kOffB + 8 * C::kBChunk + C::kBHalf);
         for (int i = threadIdx.x; i < C::kBHalf / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
         fence_proxy_async_smem();
@@ -223,13 +234,14 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_do);
-            mbar_arrive_expect_tx(bar_qdo, (kQChunks + kVChunks) * C::kBHalf);
+            mbar_arrive_expect_tx(bar_qdo, (kQChunks + (kFwd ? 0 : kVChunks)) * C::kBHalf);
             const int row0 = qg * p.h_q + NH * rank;
             const uint64_t pol_stream = l2_policy_evict_first();
             for (int j = 0; j < kQChunks; ++j)
                 tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_qdo, pol_stream);
-            for (int j = 0; j < kVChunks; ++j)
-                tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo, pol_stream);
+            if constexpr (!kFwd)
+                for (int j = 0; j < kVChunks; ++j)
+                    tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo, pol_stream);
             if (rank == 1) {
                 // -------------------------------------------------------------- forward slot-full to the even CTA
                 mbar_wait(bar_qdo, 0, wc, kErrRecompute + 16, kPollSleepNs);   // Q / dO are part of what "full" promises
@@ -240,7 +252,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 }
             } else {
                 // -------------------------------------------------------------- UMMA issuer for the pair
-                constexpr uint32_t idesc = make_idesc_bf16(256, 2 * HP, 0, 0);
+                constexpr uint32_t idesc = make_idesc_bf16(256, C::kAccCols, 0, 0);
                 mbar_wait(bar_qdo, 0, wc, kErrRecompute + 12);
                 int it = 0;
                 for (int tile = 0; tile < n_tiles; ++tile) {
@@ -270,12 +282,14 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         // ------------------------------------------------------------------ softmax gradient (own 128 keys)
         const int quarter = warp & 3;
         const int g = warp >> 2;            // head half
-        for (int h = threadIdx.x; h < HP; h += 256) {
-            const bool hv = h < p.h_q;
-            lse_s[h] = hv ? p.lse[static_cast<size_t>(qg) * p.h_q + h] * p.lse_mult : __int_as_float(0x7f800000);
-            delta_s[h] = hv ? p.delta[static_cast<size_t>(qg) * p.h_q + h] : 0.f;
+        if constexpr (!kFwd) {
+            for (int h = threadIdx.x; h < HP; h += 256) {
+                const bool hv = h < p.h_q;
+                lse_s[h] = hv ? p.lse[static_cast<size_t>(qg) * p.h_q + h] * p.lse_mult : __int_as_float(0x7f800000);
+                delta_s[h] = hv ? p.delta[static_cast<size_t>(qg) * p.h_q + h] : 0.f;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
         const int row = quarter * 32 + lane;
         const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
         const uint64_t pol_stream = l2_policy_evict_first();
@@ -287,38 +301,60 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
             if (threadIdx.x == 0) SMLA_STAMP(6, tile * kQChunks, 18);
             tc_fence_after_sync();
-            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
             const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
-            __nv_bfloat16* s_out = p.s_scr + off;
-            __nv_bfloat16* ds_out = p.ds_scr + off;
+            if constexpr (kFwd) {
+                // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
+                float* t_out = p.logits + off;
+                const float ninf = __int_as_float(0xff800000);
 #pragma unroll 1
-            for (int c0 = 0; c0 < NH; c0 += 16) {
-                uint32_t pv[16], dpv[16];
-                tmem_ld_32x16(taddr + c0, pv);
-                tmem_ld_32x16(taddr + NH + c0, dpv);
-                tmem_ld_wait();
-                uint32_t so[8], dso[8];
-                const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
-                const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
+                for (int c0 = 0; c0 < NH; c0 += 16) {
+                    uint32_t pv[16];
+                    tmem_ld_32x16(taddr + c0, pv);
+                    tmem_ld_wait();
+                    uint32_t lo[8], hi[8];
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const float4 l = l4[v], dl = d4[v];
-                    const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {dl.x, dl.y, dl.z, dl.w};
-                    float sv[4], dsv[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = 4 * v + e;
-                        const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e])) : 0.f;
-                        sv[e] = sx;
-                        dsv[e] = valid ? sx * (__uint_as_float(dpv[c]) - dv[e]) * p.sm_scale : 0.f;
+                    for (int c = 0; c < 16; ++c) {
+                        const bool keep = valid && (g * NH + c0 + c) < p.h_q;
+                        const float t = keep ? __uint_as_float(pv[c]) * p.scale_log2e : ninf;
+                        if (c < 8) lo[c] = __float_as_uint(t); else hi[c - 8] = __float_as_uint(t);
                     }
-                    so[2 * v] = pack_bf16x2(sv[0], sv[1]);
-                    so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]);
-                    dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
-                    dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
+                    st_global_v8(t_out + c0, lo);          // re-read right away by the softmax kernel: default policy
+                    st_global_v8(t_out + c0 + 8, hi);
                 }
-                st_global_v8_hint(s_out + c0, so, pol_stream);
-                st_global_v8_hint(ds_out + c0, dso, pol_stream);
+            } else {
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
+                __nv_bfloat16* s_out = p.s_scr + off;
+                __nv_bfloat16* ds_out = p.ds_scr + off;
+#pragma unroll 1
+                for (int c0 = 0; c0 < NH; c0 += 16) {
+                    uint32_t pv[16], dpv[16];
+                    tmem_ld_32x16(taddr + c0, pv);
+                    tmem_ld_32x16(taddr + NH + c0, dpv);
+                    tmem_ld_wait();
+                    uint32_t so[8], dso[8];
+                    const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
+                    const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const float4 l = l4[v], dl = d4[v];
+                        const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {dl.x, dl.y, dl.z, dl.w};
+                        float sv[4], dsv[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * v + e;
+                            const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e])) : 0.f;
+                            sv[e] = sx;
+                            dsv[e] = valid ? sx * (__uint_as_float(dpv[c]) - dv[e]) * p.sm_scale : 0.f;
+                        }
+                        so[2 * v] = pack_bf16x2(sv[0], sv[1]);
+                        so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]);
+                        dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
+                        dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
+                    }
+                    st_global_v8_hint(s_out + c0, so, pol_stream);
+                    st_global_v8_hint(ds_out + c0, dso, pol_stream);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -330,6 +366,54 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     __syncthreads();
     cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
     if (warp == 16) tmem_dealloc_2cta(tmem, C::kTmemCols);
+}
+
+// =============================================================================================
+// forward softmax: one CTA per query, thread = (head, key slice).  Reads the base-2 logits the forward
+// recompute pass left in the scratch ([key][head] fp32, -inf where masked; 1 MB per query at h128 / top-k 2048,
+// so the second sweep hits L2), writes lse and the bf16 probabilities S = exp2(t - lse) for the o = S.V kernel.
+// A query without any valid slot gets lse = +inf and S = 0 (o = 0).
+// =============================================================================================
+template <int HP>
+__global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) {
+    constexpr int kSlices = 512 / HP;
+    const int ql = blockIdx.x;
+    const int qg = p.q0 + ql;
+    const int h = threadIdx.x % HP;
+    const int sl = threadIdx.x / HP;
+    const float* t_row = p.logits + static_cast<size_t>(ql) * p.topk_pad * HP + h;
+    __shared__ float m_s[512], l_s[512];
+    const float ninf = __int_as_float(0xff800000);
+    float m = ninf, l = 0.f;
+    for (int key = sl; key < p.topk_pad; key += kSlices) {
+        const float t = t_row[static_cast<size_t>(key) * HP];
+        if (t > m) {               // online max: rescale the running sum
+            l = l * ex2_approx(m - t) + 1.f;
+            m = t;
+        } else if (t != ninf) {
+            l += ex2_approx(t - m);
+        }
+    }
+    m_s[threadIdx.x] = m;
+    l_s[threadIdx.x] = l;
+    __syncthreads();
+    float mm = ninf;
+#pragma unroll
+    for (int i = 0; i < kSlices; ++i) mm = fmaxf(mm, m_s[i * HP + h]);
+    float ll = 0.f;
+#pragma unroll
+    for (int i = 0; i < kSlices; ++i) {
+        const float mi = m_s[i * HP + h];
+        if (mi != ninf) ll += l_s[i * HP + h] * ex2_approx(mi - mm);
+    }
+    const float lse2 = (mm == ninf) ? __int_as_float(0x7f800000) : mm + __log2f(ll);
+    if (sl == 0 && h < p.h_q) p.lse_out[static_cast<size_t>(qg) * p.h_q + h] = lse2 * p.lse_out_mult;
+    __nv_bfloat16* s_row = p.s_scr + static_cast<size_t>(ql) * p.topk_pad * HP + h;
+    for (int key = sl; key < p.topk_pad; key += kSlices) {
+        const float t = t_row[static_cast<size_t>(key) * HP];
+        const float sx = (t == ninf) ? 0.f : ex2_approx(t - lse2);
+        s_row[static_cast<size_t>(key) * HP] = __float2bfloat16_rn(sx);
+    }
 }
 
 // =============================================================================================
@@ -561,9 +645,11 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     const int qg = p.q0 + ql;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n_blk = part ? 2 : 3;
-    const int chunk0 = part ? kSplitChunk : 0;
-    const int n_ch = part ? kQChunks - kSplitChunk : kSplitChunk;
+    // d-part 0 gathers kv column chunks [0, g_split), part 1 [g_split, g_total): (5, 9) for dQ, (4, 8) for o = S.V
+    const int chunk0 = part ? p.g_split : 0;
+    const int n_ch = part ? p.g_total - p.g_split : p.g_split;
+    const int n_blk = (n_ch + 1) >> 1;
+    const bool half_last = n_ch & 1;      // last block has 64 real rows
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -677,9 +763,9 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         mbar_wait(bar_acc, 0, wc, kErrDq + 3, kPollSleepNs);
         tc_fence_after_sync();
         for (int blk = 0; blk < n_blk; ++blk) {
-            if (part == 0 && blk == 2 && quarter >= 2) continue;
+            if (half_last && blk == n_blk - 1 && quarter >= 2) continue;
             const int d = chunk0 * 64 + blk * 128 + quarter * 32 + lane;
-            __nv_bfloat16* out = p.dQ + static_cast<size_t>(qg) * p.h_q * kDQK + d;
+            __nv_bfloat16* out = p.gout + static_cast<size_t>(qg) * p.h_q * p.gout_pitch + d;
             const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + blk * HP;
 #pragma unroll 1
             for (int cb = 0; cb < HP / 32; ++cb) {
@@ -689,7 +775,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int h = cb * 32 + j;
-                    if (h < p.h_q) out[static_cast<size_t>(h) * kDQK] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    if (h < p.h_q) out[static_cast<size_t>(h) * p.gout_pitch] = __float2bfloat16_rn(__uint_as_float(r[j]));
                 }
             }
         }

@@ -36,6 +36,15 @@ class _Params(ctypes.Structure):
     ]
 
 
+class _FwdParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("kv", ctypes.c_void_p), ("indices", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("lse", ctypes.c_void_p),
+        ("s_q", ctypes.c_int32), ("s_kv", ctypes.c_int32), ("h_q", ctypes.c_int32), ("topk", ctypes.c_int32),
+        ("sm_scale", ctypes.c_float), ("q_start_index_s", ctypes.c_int32), ("lse_is_base2", ctypes.c_int32),
+    ]
+
+
 class WorkspaceLayout(ctypes.Structure):
     _fields_ = [
         ("err_offset", ctypes.c_size_t), ("delta_offset", ctypes.c_size_t), ("s_offset", ctypes.c_size_t),
@@ -82,6 +91,10 @@ def load_library() -> ctypes.CDLL:
         lib.smla_bwd_noalloc_capacity.restype = ctypes.c_size_t
         lib.smla_bwd_noalloc_status.restype = ctypes.c_int
         lib.smla_bwd_noalloc_status.argtypes = [ctypes.c_void_p]
+        lib.smla_fwd_workspace_size.restype = ctypes.c_size_t
+        lib.smla_fwd_workspace_size.argtypes = [ctypes.POINTER(_FwdParams), ctypes.c_size_t]
+        lib.smla_fwd_run.restype = ctypes.c_int
+        lib.smla_fwd_run.argtypes = [ctypes.POINTER(_FwdParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
         lib.smla_bwd_last_launch_count.restype = ctypes.c_int
         lib.smla_bwd_status_string = lib.smla_status_string
         lib.smla_status_string.restype = ctypes.c_char_p
@@ -200,6 +213,65 @@ def mla_bwd(
         if check_device_status:
             _raise_status(lib, lib.smla_bwd_status(workspace.ptr, stream), "smla_bwd device status")
     return dQ, dKV
+
+
+def mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: Optional[float] = None,
+            q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True, workspace: Optional[Workspace] = None,
+            workspace_budget: int = 0, check_device_status: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sparse MLA attention forward for the same top-k indices: returns (o bf16 [s_q,h_q,512], lse fp32 [s_q,h_q]).
+
+    The reference has no forward operator; its tests make o / lse with fp32 torch code
+    (`dq_test/test_dq_phase.py:53-59`).  Defaults mirror `mla_bwd` (causal rule with query start 0, base-2
+    lse) so that `mla_bwd(q, kv, dO, lse, o, indices)` can consume the outputs directly.
+    """
+    for name, t in (("q", q), ("kv", kv), ("indices", indices)):
+        _check(isinstance(t, torch.Tensor) and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous CUDA tensor")
+    _check(q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and indices.dtype == torch.int32, "dtypes: bf16, bf16, int32")
+    _check(q.dim() == 3 and q.shape[2] == D_QK and kv.shape[-1] == D_QK, f"q [s_q,h_q,{D_QK}], kv [s_kv,{D_QK}]")
+    _check(kv.dim() == 2 or (kv.dim() == 3 and kv.shape[1] == 1), "kv must be [s_kv,576] or [s_kv,1,576]")
+    _check(indices.shape[0] == q.shape[0] and (indices.dim() == 2 or (indices.dim() == 3 and indices.shape[1] == 1)),
+           "indices must be [s_q,topk] or [s_q,1,topk]")
+    s_q, h_q, _ = q.shape
+    _check(0 < h_q <= 128 and h_q % 8 == 0, f"h_q must be a multiple of 8 in [8, 128], got {h_q}")
+    lib = load_library()
+    with torch.cuda.device(q.device):
+        o = torch.empty(s_q, h_q, D_V, dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty(s_q, h_q, dtype=torch.float32, device=q.device)
+        params = _FwdParams(q.data_ptr(), kv.data_ptr(), indices.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                            s_q, kv.shape[0], h_q, indices.shape[-1],
+                            float(sm_scale) if sm_scale is not None else 0.0,
+                            NO_CAUSAL if q_start_index_s is None else int(q_start_index_s), 1 if lse_is_base2 else 0)
+        if workspace is None:
+            need = lib.smla_fwd_workspace_size(ctypes.byref(params), workspace_budget)
+            _check(need > 0, "unsupported shapes for the sparse MLA forward")
+            workspace = Workspace(need, q.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        _raise_status(lib, lib.smla_fwd_run(ctypes.byref(params), workspace.ptr, workspace.nbytes, stream), "smla_fwd_run")
+        if check_device_status:
+            _raise_status(lib, lib.smla_bwd_status(workspace.ptr, stream), "smla_fwd device status")
+    return o, lse
+
+
+class SparseMLAFunction(torch.autograd.Function):
+    """o = sparse_mla(q, kv, indices): forward and backward both in the hand-written kernels."""
+
+    @staticmethod
+    def forward(ctx, q, kv, indices, sm_scale, q_start_index_s):
+        o, lse = mla_fwd(q, kv, indices, sm_scale=sm_scale, q_start_index_s=q_start_index_s)
+        ctx.save_for_backward(q, kv, indices, o, lse)
+        ctx.sm_scale, ctx.q_start = sm_scale, q_start_index_s
+        return o
+
+    @staticmethod
+    def backward(ctx, dO):
+        q, kv, indices, o, lse = ctx.saved_tensors
+        dq, dkv = mla_bwd(q, kv, dO.contiguous(), lse, o, indices, sm_scale=ctx.sm_scale, q_start_index_s=ctx.q_start)
+        return dq, dkv.to(kv.dtype), None, None, None
+
+
+def sparse_mla(q, kv, indices, sm_scale: Optional[float] = None, q_start_index_s: Optional[int] = 0):
+    """Differentiable sparse MLA attention (bf16 in, bf16 out; gradients for q and kv)."""
+    return SparseMLAFunction.apply(q, kv, indices, sm_scale, q_start_index_s)
 
 
 def mla_bwd_noalloc(q, kv, dO, lse, O, indices, dQ, dKV, sm_scale: Optional[float] = None,
