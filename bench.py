@@ -280,6 +280,22 @@ def run_ours(args):
             else:
                 entry["gbs"] = 2.0 * nq * w.h_q * 512 * 2 / (kms * 1e-3) / 1e9
             kernels[name] = entry
+    # the forward op of the same shapes (2176 FLOPs per slot: P and S.V), first sequence of this rank
+    forward = None
+    if seqs and not query_sharded and stages == op.STAGE_ALL:
+        s = seqs[0]
+        ts = []
+        for i in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            op.mla_fwd(s["q"], s["kv"], s["indices"], q_start_index_s=s["q_start_index_s"])
+            b.record()
+            torch.cuda.synchronize()
+            if i:
+                ts.append(a.elapsed_time(b))
+        fms = sum(ts) / len(ts)
+        forward = {"ms": fms, "tflops": 2176.0 * s["q"].shape[0] * w.h_q * w.topk / (fms * 1e-3) / 1e12,
+                   "flops_per_slot": 2176}
     peaks, peak_kind = load_peaks()
     roofline = None
     mm = {k: v for k, v in kernels.items() if "tflops" in v}
@@ -351,6 +367,8 @@ def run_ours(args):
                        "stages": stages, "l2": "inputs larger than L2 (no flush)"},
             "clocks": clocks, "gpu_launches": n_launch, "kernels": kernels,
         }
+        if forward:
+            out["forward"] = forward
         if roofline:
             out["roofline"] = roofline
         if e2e:

@@ -377,6 +377,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 template <int HP>
 __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) {
     constexpr int kSlices = 512 / HP;
+    constexpr int kBatch = 8;                 // independent loads in flight per thread
     const int ql = blockIdx.x;
     const int qg = p.q0 + ql;
     const int h = threadIdx.x % HP;
@@ -384,35 +385,47 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
     const float* t_row = p.logits + static_cast<size_t>(ql) * p.topk_pad * HP + h;
     __shared__ float m_s[512], l_s[512];
     const float ninf = __int_as_float(0xff800000);
-    float m = ninf, l = 0.f;
-    for (int key = sl; key < p.topk_pad; key += kSlices) {
-        const float t = t_row[static_cast<size_t>(key) * HP];
-        if (t > m) {               // online max: rescale the running sum
-            l = l * ex2_approx(m - t) + 1.f;
-            m = t;
-        } else if (t != ninf) {
-            l += ex2_approx(t - m);
-        }
+    // sweep 1: max (topk_pad is a multiple of 256, so every thread sees whole batches)
+    float m = ninf;
+    for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
+        float t[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) m = fmaxf(m, t[i]);
     }
     m_s[threadIdx.x] = m;
-    l_s[threadIdx.x] = l;
     __syncthreads();
     float mm = ninf;
 #pragma unroll
     for (int i = 0; i < kSlices; ++i) mm = fmaxf(mm, m_s[i * HP + h]);
+    // sweep 2 (L2 hits): sum of exp2(t - max); exp2(-inf) = 0 takes care of masked slots
+    float l = 0.f;
+    if (mm != ninf) {
+        for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
+            float t[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) l += ex2_approx(t[i] - mm);
+        }
+    }
+    l_s[threadIdx.x] = l;
+    __syncthreads();
     float ll = 0.f;
 #pragma unroll
-    for (int i = 0; i < kSlices; ++i) {
-        const float mi = m_s[i * HP + h];
-        if (mi != ninf) ll += l_s[i * HP + h] * ex2_approx(mi - mm);
-    }
+    for (int i = 0; i < kSlices; ++i) ll += l_s[i * HP + h];
     const float lse2 = (mm == ninf) ? __int_as_float(0x7f800000) : mm + __log2f(ll);
     if (sl == 0 && h < p.h_q) p.lse_out[static_cast<size_t>(qg) * p.h_q + h] = lse2 * p.lse_out_mult;
+    // sweep 3: probabilities
     __nv_bfloat16* s_row = p.s_scr + static_cast<size_t>(ql) * p.topk_pad * HP + h;
-    for (int key = sl; key < p.topk_pad; key += kSlices) {
-        const float t = t_row[static_cast<size_t>(key) * HP];
-        const float sx = (t == ninf) ? 0.f : ex2_approx(t - lse2);
-        s_row[static_cast<size_t>(key) * HP] = __float2bfloat16_rn(sx);
+    for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
+        float t[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i)
+            s_row[static_cast<size_t>(key + i * kSlices) * HP] = __float2bfloat16_rn(ex2_approx(t[i] - lse2));
     }
 }
 
