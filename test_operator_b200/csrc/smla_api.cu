@@ -142,7 +142,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     // per device, so set on every call (cheap) rather than once per process
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, false>, rp::Cfg<HP, false>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_kernel<HP>, dk::Cfg<HP>::kSmemBytes);
-    attr_ok &= set_smem(smla_dq_kernel<HP>, dq::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_dq_kernel<HP, kSplitChunk, kQChunks>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
     KParams kp{};
@@ -155,9 +155,6 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     kp.dKV = p->dKV;
     kp.dQ = reinterpret_cast<__nv_bfloat16*>(p->dQ);
     kp.gout = kp.dQ;
-    kp.gout_pitch = kDQK;
-    kp.g_split = kSplitChunk;
-    kp.g_total = kQChunks;
     kp.g_err = reinterpret_cast<int*>(ws + pl.err_off);
     kp.s_q = p->s_q;
     kp.s_kv = p->s_kv;
@@ -192,7 +189,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DQ) {
-            smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_ds, kp);
+            smla_dq_kernel<HP, kSplitChunk, kQChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_ds, kp);
             ++g_last_launches;
         }
     }
@@ -262,7 +259,8 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, true>, rp::Cfg<HP, true>::kSmemBytes);
-    attr_ok &= set_smem(smla_dq_kernel<HP>, dq::Cfg<HP>::kSmemBytes);
+    // o = S.V: the two d-parts gather V column chunks [0,4) and [4,8)
+    attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
     KParams kp{};
@@ -283,15 +281,12 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
     kp.q_start = kp.causal ? p->q_start_index_s : 0;
     kp.gout = reinterpret_cast<__nv_bfloat16*>(p->o);
-    kp.gout_pitch = kDV;
-    kp.g_split = kVChunks / 2;    // o = S.V: the two d-parts gather V column chunks [0,4) and [4,8)
-    kp.g_total = kVChunks;
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         smla_recompute_pair_kernel<HP, true><<<nq * 2, rp::kThreads, rp::Cfg<HP, true>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
         smla_fwd_softmax_kernel<HP><<<nq, 512, 0, st>>>(kp);
-        smla_dq_kernel<HP><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_s, kp);
+        smla_dq_kernel<HP, kVChunks / 2, kVChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_s, kp);
         g_last_launches += 3;
     }
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;

@@ -43,9 +43,8 @@ struct KParams {
     float* logits;            // [q_chunk, topk_pad, HP] base-2 logits, -inf where masked
     float* lse_out;           // [s_q, h_q]
     float lse_out_mult;       // 1 (base 2) or ln 2 (natural log)
-    // dq-style kernel: which column chunks of kv the two d-parts gather, and where the result goes
-    __nv_bfloat16* gout;      // [s_q, h_q, gout_pitch]
-    int gout_pitch, g_split, g_total;
+    // dq-style kernel: where the result goes (dQ with pitch 576, or o with pitch 512)
+    __nv_bfloat16* gout;      // [s_q, h_q, 576] (dQ) or [s_q, h_q, 512] (o)
     int* g_err;
     int q0;                   // first query (global row) of this pass
     int s_q, s_kv, h_q, topk, topk_pad;
@@ -254,25 +253,39 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 // -------------------------------------------------------------- UMMA issuer for the pair
                 constexpr uint32_t idesc = make_idesc_bf16(256, C::kAccCols, 0, 0);
                 mbar_wait(bar_qdo, 0, wc, kErrRecompute + 12);
-                int it = 0;
+                // This one thread feeds the tensor pipe of both SMs: 4 UMMAs (512 cycles of math) per chunk.  Its
+                // own instruction stream must stay well under that, so descriptors are kept as (low word, high
+                // word) and only the low word (the 16-byte address field) moves; slot and phase are counters.
+                const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
+                const uint32_t desc_lo = static_cast<uint32_t>(make_smem_desc(0, 16, 1024, kSwizzle128));
+                const uint32_t a_lo0 = desc_lo + ((s_base + C::kOffRing) >> 4);
+                const uint32_t b_lo0 = desc_lo + ((s_base + C::kOffB) >> 4);
+                int s = 0;
+                uint32_t ph = 0;
                 for (int tile = 0; tile < n_tiles; ++tile) {
                     const int b = tile & 1;
                     mbar_spin(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
                     tc_fence_after_sync();
                     const uint32_t d = tmem + b * C::kAccCols;
-                    for (int j = 0; j < kQChunks; ++j, ++it) {
-                        const int s = it % kStages;
-                        SMLA_STAMP(2, it, 18);
-                        mbar_spin(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 14);
-                        SMLA_STAMP(3, it, 18);
-                        const uint64_t ad = make_smem_desc(s_base + C::kOffRing + s * kChunkA, 16, 1024, kSwizzle128);
-                        const uint64_t bd = make_smem_desc(s_base + C::kOffB + j * C::kBChunk, 16, 1024, kSwizzle128);
+                    uint32_t b_lo = b_lo0;
+#pragma unroll 1
+                    for (int j = 0; j < kQChunks; ++j) {
+                        SMLA_STAMP(2, tile * kQChunks + j, 18);
+                        mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
+                        SMLA_STAMP(3, tile * kQChunks + j, 18);
+                        const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
+                        umma_ss_2cta(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)   // 32 bytes further along K = +2 in the descriptor's address field
-                            umma_ss_2cta(d, ad + 2 * k, bd + 2 * k, idesc, (j | k) != 0);
-                        SMLA_STAMP(4, it, 18);
+                        for (int k = 1; k < 4; ++k)   // 32 bytes further along K = +2 in the address field
+                            umma_ss_2cta(d, desc_hi | (a_lo + 2 * k), desc_hi | (b_lo + 2 * k), idesc, 1);
+                        SMLA_STAMP(4, tile * kQChunks + j, 18);
                         umma_commit_2cta_mask(bar_empty + 8 * s, 3);
-                        SMLA_STAMP(5, it, 18);
+                        SMLA_STAMP(5, tile * kQChunks + j, 18);
+                        b_lo += C::kBChunk >> 4;
+                        if (++s == kStages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
                     }
                     umma_commit_2cta_mask(bar_tfull + 8 * b, 3);
                 }
@@ -648,7 +661,7 @@ template <int HP> struct Cfg {
 };
 }  // namespace dq
 
-template <int HP>
+template <int HP, int kSplit, int kTotal>
 __global__ void __launch_bounds__(dq::kThreads, 1)
 smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
@@ -658,9 +671,9 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     const int qg = p.q0 + ql;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // d-part 0 gathers kv column chunks [0, g_split), part 1 [g_split, g_total): (5, 9) for dQ, (4, 8) for o = S.V
-    const int chunk0 = part ? p.g_split : 0;
-    const int n_ch = part ? p.g_total - p.g_split : p.g_split;
+    // d-part 0 gathers kv column chunks [0, kSplit), part 1 [kSplit, kTotal): (5, 9) for dQ, (4, 8) for o = S.V
+    const int chunk0 = part ? kSplit : 0;
+    const int n_ch = part ? kTotal - kSplit : kSplit;
     const int n_blk = (n_ch + 1) >> 1;
     const bool half_last = n_ch & 1;      // last block has 64 real rows
 
@@ -775,22 +788,35 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         const int quarter = warp;
         mbar_wait(bar_acc, 0, wc, kErrDq + 3, kPollSleepNs);
         tc_fence_after_sync();
+        // The accumulator has d on the lanes and heads on the columns; the output wants rows of d per head.
+        // Transpose a block through shared memory (the pipeline stages are idle by now) so that the global
+        // stores are 16-byte vectors instead of 2-byte scalars.
+        constexpr int kPitch = kTotal * 64;      // 576 for dQ, 512 for o
+        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [HP heads][128 d]
+        const int tid = threadIdx.x;             // 0..127
         for (int blk = 0; blk < n_blk; ++blk) {
-            if (half_last && blk == n_blk - 1 && quarter >= 2) continue;
-            const int d = chunk0 * 64 + blk * 128 + quarter * 32 + lane;
-            __nv_bfloat16* out = p.gout + static_cast<size_t>(qg) * p.h_q * p.gout_pitch + d;
-            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + blk * HP;
+            const int d_real = (half_last && blk == n_blk - 1) ? 64 : 128;
+            if (quarter * 32 < d_real) {
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + blk * HP;
 #pragma unroll 1
-            for (int cb = 0; cb < HP / 32; ++cb) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + cb * 32, r);
-                tmem_ld_wait();
+                for (int cb = 0; cb < HP / 32; ++cb) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + cb * 32, r);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int h = cb * 32 + j;
-                    if (h < p.h_q) out[static_cast<size_t>(h) * p.gout_pitch] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    for (int j = 0; j < 32; ++j)
+                        stg[(cb * 32 + j) * 128 + quarter * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[j]));
                 }
             }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            const int upr_log2 = d_real == 128 ? 4 : 3;      // 16 or 8 sixteen-byte units per head row
+            __nv_bfloat16* out = p.gout + static_cast<size_t>(qg) * p.h_q * kPitch + chunk0 * 64 + blk * 128;
+            for (int u = tid; u < (p.h_q << upr_log2); u += 128) {
+                const int h = u >> upr_log2, c = u & ((1 << upr_log2) - 1);
+                const uint4 v = *reinterpret_cast<const uint4*>(stg + h * 128 + c * 8);
+                *reinterpret_cast<uint4*>(out + static_cast<size_t>(h) * kPitch + c * 8) = v;
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
         }
     }
     tc_fence_before_sync();
