@@ -123,8 +123,8 @@ int smla_bwd_delta(const void* O, const void* dO, float* delta, int32_t s_q, int
 typedef struct smla_bwd_workspace_layout {
     size_t err_offset;    /* int32 device error word */
     size_t delta_offset;  /* f32 [s_q, h_q] */
-    size_t s_offset;      /* bf16 [q_chunk, topk_pad, h_pad]  S  of the LAST query chunk processed */
-    size_t ds_offset;     /* bf16 [q_chunk, topk_pad, h_pad]  dS of the LAST query chunk processed */
+    size_t s_offset;      /* bf16 [q_chunk, h_pad/8, topk_pad, 8]  S  of the LAST query chunk processed; per query: */
+    size_t ds_offset;     /* bf16 [q_chunk, h_pad/8, topk_pad, 8]  dS    block of 8 heads, key, head in block      */
     int32_t q_chunk, topk_pad, h_pad;
     size_t total_bytes;
 } smla_bwd_workspace_layout;

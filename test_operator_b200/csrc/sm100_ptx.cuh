@@ -146,6 +146,14 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap,
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_hint(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+        : "memory");
+}
 // Gather of four arbitrary rows (r0..r3) of a 2-D tensor, box-width columns starting at c0.
 // Rows land in shared memory one after another (4 x box-width bytes).
 __device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int c0, int r0, int r1, int r2, int r3,
@@ -162,6 +170,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async16_hint(uint32_t dst, const void* src, uint64_t policy) {
     asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(policy)
+                 : "memory");
+}
+// Copies `src_bytes` (0 or 16) bytes and fills the rest of the 16 with zeros: with 0 nothing is read from global.
+__device__ __forceinline__ void cp_async16_zfill_hint(uint32_t dst, const void* src, uint32_t src_bytes, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(src_bytes),
+                 "l"(policy)
                  : "memory");
 }
 // Arrive on `bar` (one pending arrival of its expected count) once every cp.async this thread has
@@ -267,6 +281,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// Same without the cluster-scope release: that release costs the issuing thread about a thousand cycles per
+// call, which a thread relaying one signal per pipeline step cannot afford.  Only for signals whose data is
+// already in place by other means: shared memory of the signalling CTA filled by copies this thread has seen
+// complete (and fenced to the async proxy), or tensor-memory reads this warp has waited for.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_2cta(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
                  : "memory");
@@ -311,6 +332,12 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
 __device__ __forceinline__ void st_global_v8_hint(void* addr, const uint32_t (&v)[8], uint64_t policy) {
     asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(addr), "r"(v[0]),
                  "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ void st_global_v4_hint(void* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                                  uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(addr), "r"(a), "r"(b), "r"(c), "r"(d),
+                 "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ void st_global_v8(void* addr, const uint32_t (&v)[8]) {

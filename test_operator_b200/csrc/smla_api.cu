@@ -57,6 +57,23 @@ bool make_map_2d(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows,
     return r == CUDA_SUCCESS;
 }
 
+// S / dS scratch [queries][h_pad/8 head blocks][topk_pad keys][8 heads] bf16 as a 4-D tensor whose rows are 32 keys
+// of one head block (512 contiguous bytes); a box takes `box_keys` keys of every head block of one query and lands
+// as [head block][keys][8 heads], the no-swizzle core-matrix order.
+bool make_map_scratch(CUtensorMap* m, const void* base, uint64_t queries, int topk_pad, int h_pad, uint32_t box_keys) {
+    EncodeFn enc = get_encode_fn();
+    if (!enc) return false;
+    const uint64_t head_blocks = uint64_t(h_pad) / 8;
+    cuuint64_t dims[4] = {256, uint64_t(topk_pad) / 32, head_blocks, queries};
+    cuuint64_t strides[3] = {512, uint64_t(topk_pad) * 16, head_blocks * uint64_t(topk_pad) * 16};
+    cuuint32_t box[4] = {256, box_keys / 32, static_cast<cuuint32_t>(head_blocks), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 struct Plan {
     int h_pad;       // heads padded to 64 or 128
     int topk_pad;    // top-k padded to a multiple of 256
@@ -124,7 +141,6 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 
     CUtensorMap tm_qnh, tm_donh, tm_qhp, tm_dohp, tm_kv, tm_s, tm_ds;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
-    const uint64_t srows = uint64_t(pl.q_chunk) * pl.topk_pad;
     bool ok = true;
     ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
     ok &= make_map_2d(&tm_donh, p->dO, kDV, qrows, kDV * 2, 64, HP / 2);
@@ -133,10 +149,10 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
     // S / dS scratch: the dkv kernel loads [128 keys x 64 heads] boxes, the dq kernel [64 keys x 64 heads]
     CUtensorMap tm_s128, tm_ds128;
-    ok &= make_map_2d(&tm_s128, s_scr, HP, srows, HP * 2, 64, 128);
-    ok &= make_map_2d(&tm_ds128, ds_scr, HP, srows, HP * 2, 64, 128);
-    ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
-    ok &= make_map_2d(&tm_ds, ds_scr, HP, srows, HP * 2, 64, 64);
+    ok &= make_map_scratch(&tm_s128, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 128);
+    ok &= make_map_scratch(&tm_ds128, ds_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 128);
+    ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
+    ok &= make_map_scratch(&tm_ds, ds_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
 
     // per device, so set on every call (cheap) rather than once per process
@@ -169,6 +185,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 #ifdef SMLA_TRACE
     kp.trace = reinterpret_cast<long long*>(ws + pl.delta_off) ;   // development builds: stamps overwrite Delta[0..512)
     kp.trace_cta = getenv("SMLA_TRACE_CTA") ? atoi(getenv("SMLA_TRACE_CTA")) : 0;
+    kp.dbg = getenv("SMLA_DBG") ? atoi(getenv("SMLA_DBG")) : 0;
 #endif
 
     if (stages & SMLA_STAGE_DELTA) {
@@ -252,11 +269,10 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
     CUtensorMap tm_qnh, tm_kv, tm_s;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
-    const uint64_t srows = uint64_t(pl.q_chunk) * pl.topk_pad;
     bool ok = true;
     ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
     ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
-    ok &= make_map_2d(&tm_s, s_scr, HP, srows, HP * 2, 64, 64);
+    ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, true>, rp::Cfg<HP, true>::kSmemBytes);
     // o = S.V: the two d-parts gather V column chunks [0,4) and [4,8)

@@ -53,14 +53,25 @@ struct KParams {
 #ifdef SMLA_TRACE
     long long* trace;         // development builds only: cycle stamps of CTA `trace_cta`
     int trace_cta;
+    int dbg;                  // development builds only: switches parts of a kernel off for timing experiments
 #endif
 };
+
+// S / dS scratch of one query: [HP/8 head blocks][topk_pad keys][8 heads] bf16, i.e. the UMMA core matrices
+// (8 keys x 16 bytes) of the no-swizzle layouts stored one after another.  A warp of the recompute kernel holds 32
+// consecutive keys, so each of its stores writes 512 consecutive bytes (four full cache lines) instead of 32
+// scattered sectors; the consumers fetch [head block][keys of a tile][8 heads] with one TMA box of 512-byte rows.
+__device__ __forceinline__ size_t scratch_offset(int key, int head, int topk_pad) {
+    return (static_cast<size_t>(head >> 3) * topk_pad + key) * 8 + (head & 7);
+}
 
 #ifdef SMLA_TRACE
 // stamp event `ev` (0..7) of step `i`, steps [lo, lo+64)
 #define SMLA_STAMP(ev, i, lo) do { if (blockIdx.x == p.trace_cta && (i) >= (lo) && (i) < (lo) + 64) p.trace[((i) - (lo)) * 8 + (ev)] = clock64(); } while (0)
+#define SMLA_DBG(bit) ((p.dbg & (bit)) != 0)
 #else
 #define SMLA_STAMP(ev, i, lo) do { } while (0)
+#define SMLA_DBG(bit) false
 #endif
 
 // error codes recorded by bounded waits: 100*kernel + site
@@ -173,7 +184,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         *s_abort = 0;
         for (int i = 0; i < kStages; ++i) {
             // the even CTA's "full" also counts one arrival forwarded from the odd CTA
-            mbar_init(bar_full + 8 * i, kProducerThreads + (rank == 0 ? 1 : 0));
+            mbar_init(bar_full + 8 * i, (SMLA_DBG(16) ? 8 : kProducerThreads) + (rank == 0 ? 1 : 0));
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_qdo, 1);
@@ -210,13 +221,18 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         const uint64_t pol_keep = l2_policy_evict_last();
         int it = 0;
         for (int tile = 0; tile < n_tiles; ++tile) {
+            // A slot whose index is out of range reads nothing and lands as zeros (its S, dS are forced to 0 anyway).
+            // Sending all of them to one stand-in row instead would make that row's cache lines a hot spot that
+            // every SM queues on.
             const char* src[4];
+            uint32_t nb[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = tile * kTileKeys + rank * 128 + r0 + 32 * i;
-                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                idx = min(max(idx, 0), p.s_kv - 1);   // unused slots gather a real row; their S, dS are forced to 0
-                src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                const bool in_range = idx >= 0 && idx < p.s_kv;
+                nb[i] = in_range ? 16u : 0u;
+                src[i] = kvb + static_cast<size_t>(in_range ? idx : 0) * (kDQK * 2);
             }
             for (int j = 0; j < kQChunks; ++j, ++it) {
                 const int s = it % kStages;
@@ -225,7 +241,11 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 if (pt == 255) SMLA_STAMP(1, it, 18);
                 const uint32_t d = dst0 + s * kChunkA;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) cp_async16_hint(d + i * 32 * 128, src[i] + j * 128, pol_keep);
+                for (int i = 0; i < 4; ++i)
+                    if (!SMLA_DBG(4)) cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
+                if (SMLA_DBG(16)) {
+                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                } else
                 cp_async_mbar_arrive_noinc(bar_full + 8 * s);
             }
         }
@@ -246,8 +266,15 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 mbar_wait(bar_qdo, 0, wc, kErrRecompute + 16, kPollSleepNs);   // Q / dO are part of what "full" promises
                 for (int it = 0; it < n_chunks; ++it) {
                     const int s = it % kStages;
+                    SMLA_STAMP(2, it, 18);
                     mbar_spin(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 17);
-                    mbar_arrive_cluster(map_to_cta(bar_full + 8 * s, 0));
+                    SMLA_STAMP(3, it, 18);
+                    if (SMLA_DBG(64)) mbar_arrive_cluster(map_to_cta(bar_full + 8 * s, 0));
+                    else {
+                    fence_proxy_async_smem();
+                    mbar_arrive_cluster_relaxed(map_to_cta(bar_full + 8 * s, 0));
+                    }
+                    SMLA_STAMP(5, it, 18);
                 }
             } else {
                 // -------------------------------------------------------------- UMMA issuer for the pair
@@ -274,10 +301,12 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
                         SMLA_STAMP(3, tile * kQChunks + j, 18);
                         const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
+                        if (!SMLA_DBG(8)) {
                         umma_ss_2cta(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
 #pragma unroll
                         for (int k = 1; k < 4; ++k)   // 32 bytes further along K = +2 in the address field
                             umma_ss_2cta(d, desc_hi | (a_lo + 2 * k), desc_hi | (b_lo + 2 * k), idesc, 1);
+                        }
                         SMLA_STAMP(4, tile * kQChunks + j, 18);
                         umma_commit_2cta_mask(bar_empty + 8 * s, 3);
                         SMLA_STAMP(5, tile * kQChunks + j, 18);
@@ -314,8 +343,8 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
             if (threadIdx.x == 0) SMLA_STAMP(6, tile * kQChunks, 18);
             tc_fence_after_sync();
-            const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
             if constexpr (kFwd) {
+                const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
                 // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
                 float* t_out = p.logits + off;
@@ -337,14 +366,21 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 }
             } else {
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
+                // the 32 lanes hold consecutive keys: 32 x 16 bytes of consecutive addresses per store
+                const size_t off = static_cast<size_t>(ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
                 __nv_bfloat16* s_out = p.s_scr + off;
                 __nv_bfloat16* ds_out = p.ds_scr + off;
 #pragma unroll 1
-                for (int c0 = 0; c0 < NH; c0 += 16) {
+                for (int c0 = 0; c0 < (SMLA_DBG(2) ? 0 : NH); c0 += 16) {
                     uint32_t pv[16], dpv[16];
+                    if (!SMLA_DBG(32)) {
                     tmem_ld_32x16(taddr + c0, pv);
                     tmem_ld_32x16(taddr + NH + c0, dpv);
                     tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) { pv[c] = c0 + c + tile; dpv[c] = c0 * c + tile; }
+                    }
                     uint32_t so[8], dso[8];
                     const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
                     const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
@@ -365,13 +401,22 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
                         dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
                     }
-                    st_global_v8_hint(s_out + c0, so, pol_stream);
-                    st_global_v8_hint(ds_out + c0, dso, pol_stream);
+                    if (!SMLA_DBG(1) || so[0] == 0x12345679u) {
+                    {   // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
+                        __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
+                        __nv_bfloat16* d0 = ds_out + static_cast<size_t>(c0) * p.topk_pad;
+                        const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
+                        st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
+                        st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
+                        st_global_v4_hint(d0, dso[0], dso[1], dso[2], dso[3], pol_stream);
+                        st_global_v4_hint(d0 + blk, dso[4], dso[5], dso[6], dso[7], pol_stream);
+                    }
+                    }
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
+            if (lane == 0) { if (SMLA_DBG(128)) mbar_arrive_cluster_relaxed(tempty0 + 8 * b); else mbar_arrive_cluster(tempty0 + 8 * b); }
             if (threadIdx.x == 0) SMLA_STAMP(7, tile * kQChunks, 18);
         }
     }
@@ -431,14 +476,14 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
     const float lse2 = (mm == ninf) ? __int_as_float(0x7f800000) : mm + __log2f(ll);
     if (sl == 0 && h < p.h_q) p.lse_out[static_cast<size_t>(qg) * p.h_q + h] = lse2 * p.lse_out_mult;
     // sweep 3: probabilities
-    __nv_bfloat16* s_row = p.s_scr + static_cast<size_t>(ql) * p.topk_pad * HP + h;
+    __nv_bfloat16* s_q = p.s_scr + static_cast<size_t>(ql) * p.topk_pad * HP;   // head-block-major layout, see scratch_offset
     for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
         float t[kBatch];
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
 #pragma unroll
         for (int i = 0; i < kBatch; ++i)
-            s_row[static_cast<size_t>(key + i * kSlices) * HP] = __float2bfloat16_rn(ex2_approx(t[i] - lse2));
+            s_q[scratch_offset(key + i * kSlices, h, p.topk_pad)] = __float2bfloat16_rn(ex2_approx(t[i] - lse2));
     }
 }
 
@@ -548,12 +593,10 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int tile = 0; tile < n_tiles; ++tile) {
                 mbar_wait(bar_sempty, (tile & 1) ^ 1, wc, kErrDkv + 1, kPollSleepNs);
                 mbar_arrive_expect_tx(bar_sfull, C::kStage);
-                const int row = ql * p.topk_pad + tile * kTileKeys;
                 const uint32_t dst = s_base + C::kOffStage;
-                for (int c = 0; c < HP / 64; ++c) {     // box = [128 keys x 64 heads]
-                    tma_load_2d_hint(dst + c * 16384, &tm_s, 64 * c, row, bar_sfull, pol_stream);
-                    tma_load_2d_hint(dst + C::kTileMat + c * 16384, &tm_ds, 64 * c, row, bar_sfull, pol_stream);
-                }
+                // box = 128 keys of every head block -> [HP/8][128 keys][8 heads]
+                tma_load_4d_hint(dst, &tm_s, 0, tile * (kTileKeys / 32), 0, ql, bar_sfull, pol_stream);
+                tma_load_4d_hint(dst + C::kTileMat, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_sfull, pol_stream);
             }
         }
     } else if (warp == 1) {
@@ -575,13 +618,11 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
-                                make_smem_desc(st_s + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
-                                ks != 0);
+                                make_smem_desc(st_s + ks * 4096, 2048, 128, kSwizzleNone), idesc, ks != 0);
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_q + ks * 2048, C::kChunk, 1024, kSwizzle128),
-                                make_smem_desc(st_ds + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, kSwizzle128), idesc,
-                                1);
+                                make_smem_desc(st_ds + ks * 4096, 2048, 128, kSwizzleNone), idesc, 1);
                     umma_commit(bar_ufull + 8 * us);
                 }
                 umma_commit(bar_sempty);
@@ -717,18 +758,20 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile % kStages;
             const char* src[2];
+            uint32_t nb[2];   // 0: slot out of range, read nothing and land zeros (no shared stand-in row: it would be a hot spot)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int key = tile * kTileKeys + r0 + 32 * i;
-                int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                idx = min(max(idx, 0), p.s_kv - 1);
-                src[i] = kvb + static_cast<size_t>(idx) * (kDQK * 2);
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                const bool in_range = idx >= 0 && idx < p.s_kv;
+                nb[i] = in_range ? 16u : 0u;
+                src[i] = kvb + static_cast<size_t>(in_range ? idx : 0) * (kDQK * 2);
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);
             const uint32_t d = dst0 + s * C::kStage;
             for (int c = kTmaChunks; c < n_ch; ++c) {
-                cp_async16_hint(d + c * 8192, src[0] + c * 128, pol_keep);
-                cp_async16_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, pol_keep);
+                cp_async16_zfill_hint(d + c * 8192, src[0] + c * 128, nb[0], pol_keep);
+                cp_async16_zfill_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, nb[1], pol_keep);
             }
             cp_async_mbar_arrive_noinc(bar_full + 8 * s);
         }
@@ -753,9 +796,8 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
             const uint32_t dst = s_base + s * C::kStage;
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
-                const int row = ql * p.topk_pad + tile * kTileKeys;
-                for (int c = 0; c < HP / 64; ++c)
-                    tma_load_2d_hint(dst + C::kKgBytes + c * 8192, &tm_ds, 64 * c, row, bar_full + 8 * s, pol_stream);
+                // box = 64 keys of every head block -> [HP/8][64 keys][8 heads]
+                tma_load_4d_hint(dst + C::kKgBytes, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_full + 8 * s, pol_stream);
             }
             __syncwarp();
             if (lane < 16) {
@@ -778,7 +820,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
 #pragma unroll
                     for (int ks = 0; ks < kTileKeys / 16; ++ks)
                         umma_ss(tmem + blk * HP, make_smem_desc(kg + 2 * blk * 8192 + ks * 2048, 8192, 1024, kSwizzle128),
-                                make_smem_desc(ds + ks * 2048, 8192, 1024, kSwizzle128), idesc, (tile | ks) != 0);
+                                make_smem_desc(ds + ks * 256, 128, 1024, kSwizzleNone), idesc, (tile | ks) != 0);
                 }
                 umma_commit(bar_empty + 8 * s);
             }

@@ -53,6 +53,20 @@ class WorkspaceLayout(ctypes.Structure):
     ]
 
 
+def scratch_matrices(ws, lay):
+    """The bf16 S and dS the recompute stage left in a workspace, as [q_chunk, topk_pad, h_pad] tensors.
+
+    In the workspace each query's matrix is stored head-block-major, [h_pad/8][topk_pad][8 heads] (what the
+    recompute kernel can write in whole cache lines and the later kernels fetch with one TMA box); this undoes
+    that for stage-by-stage checks."""
+    n = lay.q_chunk * lay.topk_pad * lay.h_pad
+    out = []
+    for off in (lay.s_offset, lay.ds_offset):
+        m = ws.buf[off: off + 2 * n].view(torch.bfloat16).view(lay.q_chunk, lay.h_pad // 8, lay.topk_pad, 8)
+        out.append(m.permute(0, 2, 1, 3).reshape(lay.q_chunk, lay.topk_pad, lay.h_pad))
+    return out[0], out[1]
+
+
 _lib = None
 _lib_lock = threading.Lock()
 

@@ -162,9 +162,7 @@ def test_stage_outputs_delta_s_ds():
     dkv = torch.empty(kv.shape, dtype=torch.float32, device=DEV)
     lay = op.run_stages(q, kv, dO, lse, O, idx, dq, dkv, ws, op.STAGE_DELTA | op.STAGE_RECOMPUTE, q_start_index_s=None)
     assert op.device_status(ws) == 0
-    n = lay.q_chunk * lay.topk_pad * lay.h_pad
-    S = ws.buf[lay.s_offset: lay.s_offset + 2 * n].view(torch.bfloat16).view(lay.q_chunk, lay.topk_pad, lay.h_pad).cpu()
-    dS = ws.buf[lay.ds_offset: lay.ds_offset + 2 * n].view(torch.bfloat16).view(lay.q_chunk, lay.topk_pad, lay.h_pad).cpu()
+    S, dS = (m.cpu() for m in op.scratch_matrices(ws, lay))
     assert torch.all(S[:, w.topk:] == 0) and torch.all(dS[:, w.topk:] == 0), "padding slots must be zero"
     # bf16 values may differ by one ulp where the fp32 value sits on a rounding boundary; dS additionally
     # carries the cancellation in (dP - Delta), so it gets an absolute term scaled by the tensor's range
