@@ -132,6 +132,38 @@ bool set_smem(K kernel, int bytes) {
     return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
 }
 
+// How many 2-CTA clusters of `kernel` the current device runs at once: the grid of a persistent kernel.  A
+// cluster needs two free SMs of one GPC, so this can be less than half the SM count.  Looked up once per device.
+template <typename K>
+int resident_pairs(K kernel, int threads, int smem_bytes) {
+    static std::mutex mu;
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] > 0) return cached[dev];
+    int n = 0;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return 0;
+        n = sms / 2;
+    }
+    cached[dev] = n;
+    return n;
+}
+
 template <int HP>
 int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages) {
     using namespace smla;
@@ -197,8 +229,11 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
+        kp.nq = nq;
         if (stages & SMLA_STAGE_RECOMPUTE) {
-            smla_recompute_pair_kernel<HP, false><<<nq * 2, rp::kThreads, rp::Cfg<HP, false>::kSmemBytes, st>>>(tm_qnh, tm_donh, kp);
+            const int pairs = resident_pairs(smla_recompute_pair_kernel<HP, false>, rp::kThreads, rp::Cfg<HP, false>::kSmemBytes);
+            if (pairs <= 0) return SMLA_ERR_LAUNCH;
+            smla_recompute_pair_kernel<HP, false><<<2 * (nq < pairs ? nq : pairs), rp::kThreads, rp::Cfg<HP, false>::kSmemBytes, st>>>(tm_qnh, tm_donh, kp);
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DKV) {
@@ -300,7 +335,10 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
-        smla_recompute_pair_kernel<HP, true><<<nq * 2, rp::kThreads, rp::Cfg<HP, true>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
+        kp.nq = nq;
+        const int pairs = resident_pairs(smla_recompute_pair_kernel<HP, true>, rp::kThreads, rp::Cfg<HP, true>::kSmemBytes);
+        if (pairs <= 0) return SMLA_ERR_LAUNCH;
+        smla_recompute_pair_kernel<HP, true><<<2 * (nq < pairs ? nq : pairs), rp::kThreads, rp::Cfg<HP, true>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
         smla_fwd_softmax_kernel<HP><<<nq, 512, 0, st>>>(kp);
         smla_dq_kernel<HP, kVChunks / 2, kVChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_s, kp);
         g_last_launches += 3;

@@ -47,6 +47,7 @@ struct KParams {
     __nv_bfloat16* gout;      // [s_q, h_q, 576] (dQ) or [s_q, h_q, 512] (o)
     int* g_err;
     int q0;                   // first query (global row) of this pass
+    int nq;                   // queries in this pass
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 }
 
 // =============================================================================================
-// recompute: one 2-CTA cluster per query, 17 warps per CTA.
+// recompute: persistent 2-CTA clusters, 19 warps per CTA; cluster c works on queries c, c + #clusters, ...
 // The pair works on 256-key tiles with cta_group::2 UMMAs of shape M = 256 keys x N = 2*HP:
 //   A  each CTA gathers ITS 128 keys of the tile (every kv row is fetched once per query, not once
 //      per head group), chunk by chunk through a 5-slot ring of [128 keys x 64 col] chunks;
@@ -124,12 +125,19 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 //      ordered (head half 0: P, dP), (head half 1: P, dP); two buffers.
 //   warps 0-7   softmax-gradient on the CTA's own keys: warp w -> TMEM lane quarter w % 4, head half w / 4
 //   warps 8-15  gather producers (cp.async 16 B, swizzled); completion arrives on the slot's mbarrier
-//   warp 16     TMA of the CTA's Q / dO chunks; in the even CTA also the UMMA issuer for the pair
-//               in the odd CTA it forwards "my slot is full" to the even CTA (cp.async cannot signal remotely)
-// Slot-free and accumulator-ready signals are tcgen05.commit arrivals delivered to both CTAs.
+//   warps 16,17 even CTA: the two UMMA issuers for the pair, taking alternate chunks.  A thread that issues a
+//               tcgen05.mma is held until the tensor pipe takes it, and whatever else it executes (barrier
+//               polls, commits) is time the pipe idles; with two threads passing a token, one waits for its
+//               next chunk and signals while the other's UMMAs run.
+//               odd CTA: warp 16 forwards "my slot is full" to the even CTA (cp.async cannot signal remotely)
+//   warp 18     TMA of the CTA's Q / dO chunks, one barrier per column chunk
+// Slot-free, chunk-free and accumulator-ready signals are tcgen05.commit arrivals delivered to both CTAs.
+// Nothing is drained between queries: the ring, the two accumulator buffers and the counters behind their
+// barrier phases run on, the Q / dO chunk j of the next query is fetched as soon as the last tile's UMMAs
+// on chunk j have finished, and the softmax of a query's last tile overlaps the next query's first UMMAs.
 // =============================================================================================
 namespace rp {
-constexpr int kThreads = 544;
+constexpr int kThreads = 608;
 constexpr int kProducerThreads = 256;
 constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;         // 16 KB gathered chunk
@@ -144,7 +152,7 @@ template <int HP, bool kFwd> struct Cfg {
     static constexpr int kOffB = 0;
     static constexpr int kOffRing = kQChunks * kBChunk;
     static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
-    static constexpr int kSmemBytes = kOffMisc + 1024 + 256 + 1024;   // lse/delta + barriers + alignment slack
+    static constexpr int kSmemBytes = kOffMisc + 1024 + 512 + 1024;   // lse/delta + barriers + alignment slack
     static constexpr int kAccCols = kFwd ? HP : 2 * HP;            // one accumulator buffer
     static constexpr int kTmemCols = 2 * kAccCols;                 // two buffers
 };
@@ -159,8 +167,8 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     constexpr int NH = C::NH;
     constexpr int kStages = C::kStages;
     const uint32_t rank = cluster_ctarank();
-    const int ql = blockIdx.x >> 1;
-    const int qg = p.q0 + ql;
+    const int pair = blockIdx.x >> 1;
+    const int n_pairs = gridDim.x >> 1;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
@@ -173,11 +181,14 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 1024);
     const uint32_t bar_full = smem_u32(bars);               // [kStages] gathered chunk landed (even CTA: in both CTAs)
     const uint32_t bar_empty = bar_full + 8 * kStages;      // [kStages] pair UMMAs reading the slot finished
-    const uint32_t bar_qdo = bar_empty + 8 * kStages;       // 1
-    const uint32_t bar_tfull = bar_qdo + 8;                 // [2] accumulator buffer complete
+    const uint32_t bar_bfull = bar_empty + 8 * kStages;     // [9] Q / dO column chunk of the current query landed
+    const uint32_t bar_bfree = bar_bfull + 8 * kQChunks;    // [9] the query's last UMMAs on the chunk finished
+    const uint32_t bar_tfull = bar_bfree + 8 * kQChunks;    // [2] accumulator buffer complete
     const uint32_t bar_tempty = bar_tfull + 16;             // [2] (even CTA) both CTAs have read the buffer
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 5));
+    const uint32_t bar_token = bar_tempty + 16;             // [2] (even CTA) issuer x may issue its next chunk
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 6));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 6) + 8 <= 512, "barrier area");
     const WaitCtx wc{p.g_err, s_abort};
 
     if (threadIdx.x == 0) {
@@ -187,14 +198,18 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             mbar_init(bar_full + 8 * i, (SMLA_DBG(16) ? 8 : kProducerThreads) + (rank == 0 ? 1 : 0));
             mbar_init(bar_empty + 8 * i, 1);
         }
-        mbar_init(bar_qdo, 1);
+        for (int i = 0; i < kQChunks; ++i) {
+            mbar_init(bar_bfull + 8 * i, 1);
+            mbar_init(bar_bfree + 8 * i, 1);
+        }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
             mbar_init(bar_tempty + 8 * i, 16);   // 8 softmax warps in each CTA
+            mbar_init(bar_token + 8 * i, 1);
         }
         fence_mbar_init();
     }
-    if constexpr (!kFwd) {   // zero block standing in for the dO half of column chunk 8
+    if constexpr (!kFwd) {   // zero block standing in for the dO half of column chunk 8 (never overwritten)
         uint4* z = reinterpret_cast<uint4*>(smem + C::kOffB + 8 * C::kBChunk + C::kBHalf);
         for (int i = threadIdx.x; i < C::kBHalf / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
         fence_proxy_async_smem();
@@ -209,7 +224,15 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
-    const int n_chunks = n_tiles * kQChunks;
+    const int nq = p.nq;
+#ifdef SMLA_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == p.trace_cta) {
+        unsigned long long gtime;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gtime));
+        p.trace[504] = clock64();
+        p.trace[505] = static_cast<long long>(gtime);
+    }
+#endif
 
     if (warp >= 8 && warp < 16) {
         // ------------------------------------------------------------------ gather producers
@@ -219,104 +242,164 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
-        int it = 0;
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            // A slot whose index is out of range reads nothing and lands as zeros (its S, dS are forced to 0 anyway).
-            // Sending all of them to one stand-in row instead would make that row's cache lines a hot spot that
-            // every SM queues on.
-            const char* src[4];
-            uint32_t nb[4];
+        // index of slot (tile, row i) of query ql, -1 past the top-k; the loads for the next tile are issued
+        // before the current tile's copies so that their latency never stalls the ring
+        auto load_idx = [&](int ql, int tile, int (&idx)[4]) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = tile * kTileKeys + rank * 128 + r0 + 32 * i;
-                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                const bool in_range = idx >= 0 && idx < p.s_kv;
-                nb[i] = in_range ? 16u : 0u;
-                src[i] = kvb + static_cast<size_t>(in_range ? idx : 0) * (kDQK * 2);
+                idx[i] = (ql < nq && key < p.topk)
+                             ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
             }
-            for (int j = 0; j < kQChunks; ++j, ++it) {
-                const int s = it % kStages;
-                mbar_spin(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, wc, kErrRecompute + 11);
-                if (pt == 0) SMLA_STAMP(0, it, 18);
-                if (pt == 255) SMLA_STAMP(1, it, 18);
-                const uint32_t d = dst0 + s * kChunkA;
+        };
+        int idx_next[4];
+        load_idx(pair, 0, idx_next);
+        int s = 0;
+        uint32_t ph = 1;                    // parity that means "slot free" for the current pass over the ring
+        for (int ql = pair; ql < nq; ql += n_pairs) {
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                // A slot whose index is out of range reads nothing and lands as zeros (its S, dS are forced to 0
+                // anyway).  Sending all of them to one stand-in row instead would make that row's cache lines a
+                // hot spot that every SM queues on.
+                const char* src[4];
+                uint32_t nb[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (!SMLA_DBG(4)) cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
-                if (SMLA_DBG(16)) {
-                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
-                } else
-                cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+                for (int i = 0; i < 4; ++i) {
+                    const bool in_range = idx_next[i] >= 0 && idx_next[i] < p.s_kv;
+                    nb[i] = in_range ? 16u : 0u;
+                    src[i] = kvb + static_cast<size_t>(in_range ? idx_next[i] : 0) * (kDQK * 2);
+                }
+                if (tile + 1 < n_tiles) load_idx(ql, tile + 1, idx_next);
+                else load_idx(ql + n_pairs, 0, idx_next);
+                for (int j = 0; j < kQChunks; ++j) {
+                    if (SMLA_DBG(2048)) {
+                        if (lane == 0) mbar_wait(bar_empty + 8 * s, ph, wc, kErrRecompute + 11, kPollSleepNs);
+                        __syncwarp();
+                    } else
+                    mbar_wait(bar_empty + 8 * s, ph, wc, kErrRecompute + 11, kPollSleepNs);
+#ifdef SMLA_TRACE
+                    if (pt == 0 && ql == pair) SMLA_STAMP(0, tile * kQChunks + j, 18);
+                    if (pt == 255 && ql == pair) SMLA_STAMP(1, tile * kQChunks + j, 18);
+#endif
+                    const uint32_t d = dst0 + s * kChunkA;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (!SMLA_DBG(4)) cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
+                    if (SMLA_DBG(16)) {
+                        if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                    } else
+                    cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+                    if (++s == kStages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
             }
         }
-    } else if (warp == 16) {
+    } else if (warp == 18) {
+        // ------------------------------------------------------------------ Q / dO chunks of this CTA's heads
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_do);
-            mbar_arrive_expect_tx(bar_qdo, (kQChunks + (kFwd ? 0 : kVChunks)) * C::kBHalf);
-            const int row0 = qg * p.h_q + NH * rank;
             const uint64_t pol_stream = l2_policy_evict_first();
-            for (int j = 0; j < kQChunks; ++j)
-                tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_qdo, pol_stream);
-            if constexpr (!kFwd)
-                for (int j = 0; j < kVChunks; ++j)
-                    tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0, bar_qdo, pol_stream);
+            uint32_t qpar = 1;              // parity of "chunk free" left by the previous query
+            for (int ql = pair; ql < nq; ql += n_pairs, qpar ^= 1) {
+                const int row0 = (p.q0 + ql) * p.h_q + NH * rank;
+                for (int j = 0; j < kQChunks; ++j) {
+                    if (ql != pair) mbar_wait(bar_bfree + 8 * j, qpar, wc, kErrRecompute + 16, kPollSleepNs);
+                    const bool with_do = !kFwd && j < kVChunks;
+                    mbar_arrive_expect_tx(bar_bfull + 8 * j, (with_do ? 2 : 1) * C::kBHalf);
+                    tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_bfull + 8 * j, pol_stream);
+                    if (with_do)
+                        tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk + C::kBHalf, &tm_do, 64 * j, row0,
+                                         bar_bfull + 8 * j, pol_stream);
+                }
+            }
+        }
+    } else if (warp == 16 || warp == 17) {
+        if (lane == 0) {
             if (rank == 1) {
+                if (warp == 16) {
                 // -------------------------------------------------------------- forward slot-full to the even CTA
-                mbar_wait(bar_qdo, 0, wc, kErrRecompute + 16, kPollSleepNs);   // Q / dO are part of what "full" promises
-                for (int it = 0; it < n_chunks; ++it) {
-                    const int s = it % kStages;
-                    SMLA_STAMP(2, it, 18);
-                    mbar_spin(bar_full + 8 * s, (it / kStages) & 1, wc, kErrRecompute + 17);
-                    SMLA_STAMP(3, it, 18);
-                    if (SMLA_DBG(64)) mbar_arrive_cluster(map_to_cta(bar_full + 8 * s, 0));
-                    else {
-                    fence_proxy_async_smem();
-                    mbar_arrive_cluster_relaxed(map_to_cta(bar_full + 8 * s, 0));
+                int s = 0;
+                uint32_t ph = 0, qpar = 0;
+                for (int ql = pair; ql < nq; ql += n_pairs, qpar ^= 1) {
+                    for (int tile = 0; tile < n_tiles; ++tile) {
+                        for (int j = 0; j < kQChunks; ++j) {
+                            // this CTA's half of Q / dO is part of what "full" promises
+                            if (tile == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrRecompute + 15);
+                            mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 17);
+                            // The copies have landed in this CTA's shared memory (the wait above saw them complete);
+                            // make them visible to the tensor core's proxy here, then signal without a cluster-scope
+                            // release, which would cost this thread about a thousand cycles per chunk.
+                            fence_proxy_async_smem();
+                            mbar_arrive_cluster_relaxed(map_to_cta(bar_full + 8 * s, 0));
+                            if (++s == kStages) {
+                                s = 0;
+                                ph ^= 1;
+                            }
+                        }
                     }
-                    SMLA_STAMP(5, it, 18);
+                }
                 }
             } else {
-                // -------------------------------------------------------------- UMMA issuer for the pair
+                // -------------------------------------------------------------- UMMA issuers for the pair
+                // Issuer x takes the chunks whose running number is x mod 2.  For a chunk it waits until the data
+                // is there, then for the token (the other issuer has issued the chunk before), issues 4 UMMAs
+                // (512 cycles of math on both SMs), passes the token on and commits.  The UMMAs of one accumulator
+                // form a dependency chain, so the commit behind a tile's last chunk covers the whole tile.
+                const int x = warp - 16;
                 constexpr uint32_t idesc = make_idesc_bf16(256, C::kAccCols, 0, 0);
-                mbar_wait(bar_qdo, 0, wc, kErrRecompute + 12);
-                // This one thread feeds the tensor pipe of both SMs: 4 UMMAs (512 cycles of math) per chunk.  Its
-                // own instruction stream must stay well under that, so descriptors are kept as (low word, high
-                // word) and only the low word (the 16-byte address field) moves; slot and phase are counters.
                 const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
                 const uint32_t desc_lo = static_cast<uint32_t>(make_smem_desc(0, 16, 1024, kSwizzle128));
                 const uint32_t a_lo0 = desc_lo + ((s_base + C::kOffRing) >> 4);
                 const uint32_t b_lo0 = desc_lo + ((s_base + C::kOffB) >> 4);
-                int s = 0;
+                const int n_queries = (nq - pair + n_pairs - 1) / n_pairs;
+                const int total = n_queries * n_tiles * kQChunks;
+                int j = x, tile = 0, gt = 0;    // chunk `it` = column chunk j of tile `tile` of the pair's query `qpar`-th; gt counts tiles
+                uint32_t qpar = 0;
+                int s = x % kStages;
                 uint32_t ph = 0;
-                for (int tile = 0; tile < n_tiles; ++tile) {
-                    const int b = tile & 1;
-                    mbar_spin(bar_tempty + 8 * b, ((tile >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
+                uint32_t k = 0;                 // chunks this issuer has done
+                for (int it = x; it < total; it += 2, ++k) {
+                    const int b = gt & 1;
+                    if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gt >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
+                    if (tile == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrRecompute + 12);
+                    if (x == 0) SMLA_STAMP(2, it, 18);
+                    mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
+                    if (x == 0) SMLA_STAMP(3, it, 18);
+                    if (it > 0) mbar_spin(bar_token + 8 * x, (x ? k : k - 1) & 1, wc, kErrRecompute + 19);
                     tc_fence_after_sync();
+                    if (x == 0) SMLA_STAMP(4, it, 18);
                     const uint32_t d = tmem + b * C::kAccCols;
-                    uint32_t b_lo = b_lo0;
-#pragma unroll 1
-                    for (int j = 0; j < kQChunks; ++j) {
-                        SMLA_STAMP(2, tile * kQChunks + j, 18);
-                        mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
-                        SMLA_STAMP(3, tile * kQChunks + j, 18);
-                        const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
-                        if (!SMLA_DBG(8)) {
-                        umma_ss_2cta(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
+                    const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
+                    const uint32_t b_lo = b_lo0 + j * (C::kBChunk >> 4);
+                    if (!SMLA_DBG(8)) {
+                    umma_ss_2cta(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
 #pragma unroll
-                        for (int k = 1; k < 4; ++k)   // 32 bytes further along K = +2 in the address field
-                            umma_ss_2cta(d, desc_hi | (a_lo + 2 * k), desc_hi | (b_lo + 2 * k), idesc, 1);
-                        }
-                        SMLA_STAMP(4, tile * kQChunks + j, 18);
-                        umma_commit_2cta_mask(bar_empty + 8 * s, 3);
-                        SMLA_STAMP(5, tile * kQChunks + j, 18);
-                        b_lo += C::kBChunk >> 4;
-                        if (++s == kStages) {
-                            s = 0;
-                            ph ^= 1;
+                    for (int kk = 1; kk < 4; ++kk)   // 32 bytes further along K = +2 in the address field
+                        umma_ss_2cta(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_token + 8 * (x ^ 1));
+                    if (x == 0) SMLA_STAMP(5, it, 18);
+                    umma_commit_2cta_mask(bar_empty + 8 * s, 3);
+                    if (tile == n_tiles - 1) umma_commit_2cta_mask(bar_bfree + 8 * j, 3);   // the next query's chunk may come in
+                    if (j == kQChunks - 1) umma_commit_2cta_mask(bar_tfull + 8 * b, 3);
+                    j += 2;
+                    if (j >= kQChunks) {
+                        j -= kQChunks;
+                        ++gt;
+                        if (++tile == n_tiles) {
+                            tile = 0;
+                            qpar ^= 1;
                         }
                     }
-                    umma_commit_2cta_mask(bar_tfull + 8 * b, 3);
+                    s += 2;
+                    if (s >= kStages) {
+                        s -= kStages;
+                        ph ^= 1;
+                    }
                 }
             }
         }
@@ -324,104 +407,120 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         // ------------------------------------------------------------------ softmax gradient (own 128 keys)
         const int quarter = warp & 3;
         const int g = warp >> 2;            // head half
-        if constexpr (!kFwd) {
-            for (int h = threadIdx.x; h < HP; h += 256) {
-                const bool hv = h < p.h_q;
-                lse_s[h] = hv ? p.lse[static_cast<size_t>(qg) * p.h_q + h] * p.lse_mult : __int_as_float(0x7f800000);
-                delta_s[h] = hv ? p.delta[static_cast<size_t>(qg) * p.h_q + h] : 0.f;
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-        }
         const int row = quarter * 32 + lane;
         const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
         const uint64_t pol_stream = l2_policy_evict_first();
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            const int key = tile * kTileKeys + rank * 128 + row;
-            const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-            const bool valid = slot_valid(idx, qg, p);
-            const int b = tile & 1;
-            mbar_wait(bar_tfull + 8 * b, (tile >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
-            if (threadIdx.x == 0) SMLA_STAMP(6, tile * kQChunks, 18);
-            tc_fence_after_sync();
-            if constexpr (kFwd) {
-                const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
-                // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order
-                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
-                float* t_out = p.logits + off;
-                const float ninf = __int_as_float(0xff800000);
-#pragma unroll 1
-                for (int c0 = 0; c0 < NH; c0 += 16) {
-                    uint32_t pv[16];
-                    tmem_ld_32x16(taddr + c0, pv);
-                    tmem_ld_wait();
-                    uint32_t lo[8], hi[8];
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const bool keep = valid && (g * NH + c0 + c) < p.h_q;
-                        const float t = keep ? __uint_as_float(pv[c]) * p.scale_log2e : ninf;
-                        if (c < 8) lo[c] = __float_as_uint(t); else hi[c - 8] = __float_as_uint(t);
-                    }
-                    st_global_v8(t_out + c0, lo);          // re-read right away by the softmax kernel: default policy
-                    st_global_v8(t_out + c0 + 8, hi);
-                }
-            } else {
-                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
-                // the 32 lanes hold consecutive keys: 32 x 16 bytes of consecutive addresses per store
-                const size_t off = static_cast<size_t>(ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
-                __nv_bfloat16* s_out = p.s_scr + off;
-                __nv_bfloat16* ds_out = p.ds_scr + off;
-#pragma unroll 1
-                for (int c0 = 0; c0 < (SMLA_DBG(2) ? 0 : NH); c0 += 16) {
-                    uint32_t pv[16], dpv[16];
-                    if (!SMLA_DBG(32)) {
-                    tmem_ld_32x16(taddr + c0, pv);
-                    tmem_ld_32x16(taddr + NH + c0, dpv);
-                    tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) { pv[c] = c0 + c + tile; dpv[c] = c0 * c + tile; }
-                    }
-                    uint32_t so[8], dso[8];
-                    const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
-                    const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const float4 l = l4[v], dl = d4[v];
-                        const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {dl.x, dl.y, dl.z, dl.w};
-                        float sv[4], dsv[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int c = 4 * v + e;
-                            const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e])) : 0.f;
-                            sv[e] = sx;
-                            dsv[e] = valid ? sx * (__uint_as_float(dpv[c]) - dv[e]) * p.sm_scale : 0.f;
-                        }
-                        so[2 * v] = pack_bf16x2(sv[0], sv[1]);
-                        so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]);
-                        dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
-                        dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
-                    }
-                    if (!SMLA_DBG(1) || so[0] == 0x12345679u) {
-                    {   // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
-                        __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
-                        __nv_bfloat16* d0 = ds_out + static_cast<size_t>(c0) * p.topk_pad;
-                        const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
-                        st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
-                        st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
-                        st_global_v4_hint(d0, dso[0], dso[1], dso[2], dso[3], pol_stream);
-                        st_global_v4_hint(d0 + blk, dso[4], dso[5], dso[6], dso[7], pol_stream);
-                    }
-                    }
-                }
+        // lse (threads 0..HP-1) and Delta (threads HP..2HP-1) of a query go through shared memory; the value for
+        // the next query is fetched one query ahead
+        const int t = threadIdx.x;
+        auto load_stat = [&](int ql) -> float {
+            if (kFwd || ql >= nq) return 0.f;
+            const int h = t < HP ? t : t - HP;
+            if (t >= 2 * HP) return 0.f;
+            if (h >= p.h_q) return t < HP ? __int_as_float(0x7f800000) : 0.f;
+            const size_t o = static_cast<size_t>(p.q0 + ql) * p.h_q + h;
+            return t < HP ? p.lse[o] * p.lse_mult : p.delta[o];
+        };
+        float stat_next = load_stat(pair);
+        int gt = 0;
+        for (int ql = pair; ql < nq; ql += n_pairs) {
+            const int qg = p.q0 + ql;
+            if constexpr (!kFwd) {
+                asm volatile("bar.sync 1, 256;" ::: "memory");      // every softmax warp is done with the previous query
+                if (t < 2 * HP) lse_s[t] = stat_next;              // delta_s follows lse_s
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                stat_next = load_stat(ql + n_pairs);
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) { if (SMLA_DBG(128)) mbar_arrive_cluster_relaxed(tempty0 + 8 * b); else mbar_arrive_cluster(tempty0 + 8 * b); }
-            if (threadIdx.x == 0) SMLA_STAMP(7, tile * kQChunks, 18);
+            for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
+                const int key = tile * kTileKeys + rank * 128 + row;
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                const bool valid = slot_valid(idx, qg, p);
+                const int b = gt & 1;
+                mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
+                if (threadIdx.x == 0) SMLA_STAMP(6, gt * kQChunks, 18);
+                tc_fence_after_sync();
+                if constexpr (kFwd) {
+                    const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
+                    // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order
+                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
+                    float* t_out = p.logits + off;
+                    const float ninf = __int_as_float(0xff800000);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < NH; c0 += 16) {
+                        uint32_t pv[16];
+                        tmem_ld_32x16(taddr + c0, pv);
+                        tmem_ld_wait();
+                        uint32_t lo[8], hi[8];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const bool keep = valid && (g * NH + c0 + c) < p.h_q;
+                            const float tv = keep ? __uint_as_float(pv[c]) * p.scale_log2e : ninf;
+                            if (c < 8) lo[c] = __float_as_uint(tv); else hi[c - 8] = __float_as_uint(tv);
+                        }
+                        st_global_v8(t_out + c0, lo);          // re-read right away by the softmax kernel: default policy
+                        st_global_v8(t_out + c0 + 8, hi);
+                    }
+                } else {
+                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
+                    // the 32 lanes hold consecutive keys: 32 x 16 bytes of consecutive addresses per store
+                    const size_t off = static_cast<size_t>(ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
+                    __nv_bfloat16* s_out = p.s_scr + off;
+                    __nv_bfloat16* ds_out = p.ds_scr + off;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < (SMLA_DBG(2) ? 0 : NH); c0 += 16) {
+                        uint32_t pv[16], dpv[16];
+                        tmem_ld_32x16(taddr + c0, pv);
+                        tmem_ld_32x16(taddr + NH + c0, dpv);
+                        tmem_ld_wait();
+                        uint32_t so[8], dso[8];
+                        const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
+                        const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const float4 l = l4[v], dl = d4[v];
+                            const float lv[4] = {l.x, l.y, l.z, l.w}, dv[4] = {dl.x, dl.y, dl.z, dl.w};
+                            float sv[4], dsv[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int c = 4 * v + e;
+                                const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e])) : 0.f;
+                                sv[e] = sx;
+                                dsv[e] = valid ? sx * (__uint_as_float(dpv[c]) - dv[e]) * p.sm_scale : 0.f;
+                            }
+                            so[2 * v] = pack_bf16x2(sv[0], sv[1]);
+                            so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]);
+                            dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
+                            dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
+                        }
+                        if (!SMLA_DBG(1) || so[0] == 0x12345679u) {
+                            // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
+                            __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
+                            __nv_bfloat16* d0 = ds_out + static_cast<size_t>(c0) * p.topk_pad;
+                            const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
+                            st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
+                            st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
+                            st_global_v4_hint(d0, dso[0], dso[1], dso[2], dso[3], pol_stream);
+                            st_global_v4_hint(d0 + blk, dso[4], dso[5], dso[6], dso[7], pol_stream);
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
+                if (threadIdx.x == 0) SMLA_STAMP(7, gt * kQChunks, 18);
+            }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
+#ifdef SMLA_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == p.trace_cta) {
+        unsigned long long gtime;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gtime));
+        p.trace[506] = clock64();
+        p.trace[507] = static_cast<long long>(gtime);
+    }
+#endif
     cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
     if (warp == 16) tmem_dealloc_2cta(tmem, C::kTmemCols);
 }
