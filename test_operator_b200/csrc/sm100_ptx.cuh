@@ -105,6 +105,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     return mbar_wait_slow(bar, parity, ctx, code, sleep_ns);
 }
 
+// ---- plain shared-memory counter as a hand-over between two threads of a CTA ------------------------------
+// An mbarrier arrival takes ~180 cycles to become visible to a poller; a volatile word takes a few tens.
+__device__ __forceinline__ void flag_store(uint32_t saddr, uint32_t v) {
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t flag_load(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr) : "memory");
+    return v;
+}
+// Bounded wait until the counter at `saddr` reaches `want` (counters only grow).
+__device__ __noinline__ bool flag_wait_slow(uint32_t saddr, uint32_t want, const WaitCtx& ctx, int code) {
+    const long long t0 = clock64();
+    int it = 0;
+    while (true) {
+        if (static_cast<int32_t>(flag_load(saddr) - want) >= 0) return true;
+        if ((++it & 255) == 0) {
+            if (*ctx.s_abort) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *ctx.s_abort = 1;
+                atomicCAS(ctx.g_err, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool flag_wait(uint32_t saddr, uint32_t want, const WaitCtx& ctx, int code) {
+    if (static_cast<int32_t>(flag_load(saddr) - want) >= 0) return true;
+    return flag_wait_slow(saddr, want, ctx, code);
+}
+
 // ---- proxies / fences -------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -360,6 +391,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+// The same under a predicate inside one asm block (`row` >= 0), so that a run of them compiles to predicated
+// instructions and not to a chain of branches around each one.
+__device__ __forceinline__ void red_add_f32_if_row(float* addr, float v, int row) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ge.s32 p, %2, 0;\n\t"
+        "@p red.global.add.f32 [%0], %1;\n\t}"
+        ::"l"(addr), "f"(v), "r"(row)
+        : "memory");
 }
 
 }  // namespace smla

@@ -48,6 +48,7 @@ struct KParams {
     int* g_err;
     int q0;                   // first query (global row) of this pass
     int nq;                   // queries in this pass
+    int split0;               // dkv / dq kernels: CTAs [0, split0) take d-part 0, the others d-part 1
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
@@ -127,8 +128,8 @@ __global__ void __launch_bounds__(256) smla_delta_kernel(const uint4* __restrict
 //   warps 8-15  gather producers (cp.async 16 B, swizzled); completion arrives on the slot's mbarrier
 //   warps 16,17 even CTA: the two UMMA issuers for the pair, taking alternate chunks.  A thread that issues a
 //               tcgen05.mma is held until the tensor pipe takes it, and whatever else it executes (barrier
-//               polls, commits) is time the pipe idles; with two threads passing a token, one waits for its
-//               next chunk and signals while the other's UMMAs run.
+//               polls, commits) is time the pipe idles; with two threads handing over through a counter, one
+//               waits for its next chunk and commits while the other's UMMAs run.
 //               odd CTA: warp 16 forwards "my slot is full" to the even CTA (cp.async cannot signal remotely)
 //   warp 18     TMA of the CTA's Q / dO chunks, one barrier per column chunk
 // Slot-free, chunk-free and accumulator-ready signals are tcgen05.commit arrivals delivered to both CTAs.
@@ -185,14 +186,15 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const uint32_t bar_bfree = bar_bfull + 8 * kQChunks;    // [9] the query's last UMMAs on the chunk finished
     const uint32_t bar_tfull = bar_bfree + 8 * kQChunks;    // [2] accumulator buffer complete
     const uint32_t bar_tempty = bar_tfull + 16;             // [2] (even CTA) both CTAs have read the buffer
-    const uint32_t bar_token = bar_tempty + 16;             // [2] (even CTA) issuer x may issue its next chunk
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 6));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 4));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    static_assert(8 * (2 * kStages + 2 * kQChunks + 6) + 8 <= 512, "barrier area");
+    const uint32_t tok = smem_u32(tmem_slot + 2);           // (even CTA) chunks issued so far, the issuers' hand-over
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 4) + 16 <= 512, "barrier area");
     const WaitCtx wc{p.g_err, s_abort};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
+        tmem_slot[2] = 0;
         for (int i = 0; i < kStages; ++i) {
             // the even CTA's "full" also counts one arrival forwarded from the odd CTA
             mbar_init(bar_full + 8 * i, (SMLA_DBG(16) ? 8 : kProducerThreads) + (rank == 0 ? 1 : 0));
@@ -205,7 +207,6 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
             mbar_init(bar_tempty + 8 * i, 16);   // 8 softmax warps in each CTA
-            mbar_init(bar_token + 8 * i, 1);
         }
         fence_mbar_init();
     }
@@ -344,10 +345,12 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 }
             } else {
                 // -------------------------------------------------------------- UMMA issuers for the pair
-                // Issuer x takes the chunks whose running number is x mod 2.  For a chunk it waits until the data
-                // is there, then for the token (the other issuer has issued the chunk before), issues 4 UMMAs
-                // (512 cycles of math on both SMs), passes the token on and commits.  The UMMAs of one accumulator
-                // form a dependency chain, so the commit behind a tile's last chunk covers the whole tile.
+                // Issuer x takes the chunks whose running number is x mod 2.  For a chunk it waits until the data is
+                // there, then until the other issuer has issued the chunk before (a counter in shared memory: the
+                // UMMAs enter the pipe in chunk order, so every accumulator is summed in one fixed order and the
+                // results are reproducible bit for bit), issues 4 UMMAs (512 cycles of math on both SMs), bumps the
+                // counter and commits.  The UMMAs of one accumulator form a dependency chain, so the commit behind a
+                // tile's last chunk covers the whole tile.
                 const int x = warp - 16;
                 constexpr uint32_t idesc = make_idesc_bf16(256, C::kAccCols, 0, 0);
                 const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
@@ -356,19 +359,18 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const uint32_t b_lo0 = desc_lo + ((s_base + C::kOffB) >> 4);
                 const int n_queries = (nq - pair + n_pairs - 1) / n_pairs;
                 const int total = n_queries * n_tiles * kQChunks;
-                int j = x, tile = 0, gt = 0;    // chunk `it` = column chunk j of tile `tile` of the pair's query `qpar`-th; gt counts tiles
+                int j = x, tile = 0, gt = 0;    // running chunk `it` = column chunk j of tile `tile` of a query; gt counts tiles
                 uint32_t qpar = 0;
                 int s = x % kStages;
                 uint32_t ph = 0;
-                uint32_t k = 0;                 // chunks this issuer has done
-                for (int it = x; it < total; it += 2, ++k) {
+                for (int it = x; it < total; it += 2) {
                     const int b = gt & 1;
                     if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gt >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
                     if (tile == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrRecompute + 12);
                     if (x == 0) SMLA_STAMP(2, it, 18);
                     mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
                     if (x == 0) SMLA_STAMP(3, it, 18);
-                    if (it > 0) mbar_spin(bar_token + 8 * x, (x ? k : k - 1) & 1, wc, kErrRecompute + 19);
+                    flag_wait(tok, static_cast<uint32_t>(it), wc, kErrRecompute + 19);
                     tc_fence_after_sync();
                     if (x == 0) SMLA_STAMP(4, it, 18);
                     const uint32_t d = tmem + b * C::kAccCols;
@@ -381,7 +383,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         umma_ss_2cta(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
                     }
                     tc_fence_before_sync();
-                    mbar_arrive(bar_token + 8 * (x ^ 1));
+                    flag_store(tok, static_cast<uint32_t>(it + 1));
                     if (x == 0) SMLA_STAMP(5, it, 18);
                     umma_commit_2cta_mask(bar_empty + 8 * s, 3);
                     if (tile == n_tiles - 1) umma_commit_2cta_mask(bar_bfree + 8 * j, 3);   // the next query's chunk may come in
@@ -449,7 +451,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     for (int c0 = 0; c0 < NH; c0 += 16) {
                         uint32_t pv[16];
                         tmem_ld_32x16(taddr + c0, pv);
-                        tmem_ld_wait();
+                        if (!SMLA_DBG(32)) tmem_ld_wait();
                         uint32_t lo[8], hi[8];
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
@@ -471,7 +473,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         uint32_t pv[16], dpv[16];
                         tmem_ld_32x16(taddr + c0, pv);
                         tmem_ld_32x16(taddr + NH + c0, dpv);
-                        tmem_ld_wait();
+                        if (!SMLA_DBG(32)) tmem_ld_wait();
                         uint32_t so[8], dso[8];
                         const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
                         const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
@@ -587,7 +589,8 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
 }
 
 // =============================================================================================
-// dkv: one CTA per (query, d-part).  d-part 0 owns columns [0,320), part 1 owns [320,576).
+// dkv: persistent CTAs, each working through (query, d-part) items of one d-part.  d-part 0 owns columns [0,320),
+// part 1 owns [320,576).
 //   resident   Q^T and dO^T of the part: chunks [HP heads x 64 d] read MN-major as the A operand
 //              (M = d, 128 rows = two adjacent chunks, K = heads)
 //   warp 0     producer: resident chunks once, then per 128-key tile the S and dS scratch tiles
@@ -596,8 +599,8 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
 //              into a ring of four 128-column TMEM units, so the MMAs run ahead of the drain
 //   warps 2-9  drain: thread = d row, each warp owns 32 d rows x 64 keys of a unit; one fp32 reduction
 //              per key, 32 lanes -> 128 contiguous bytes of dKV
-// Part 0's third block has 64 real rows (d 256..319); its upper 64 rows read whatever follows
-// in shared memory and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
+// Part 0's third block has 64 real rows (d 256..319); its other 64 rows read a neighbouring chunk
+// and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
 // =============================================================================================
 namespace dk {
 constexpr int kThreads = 320;   // warp 0 producer, warp 1 UMMA issuer, warps 2-9 drain
@@ -623,9 +626,12 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dk;
     using C = Cfg<HP>;
-    const int part = blockIdx.x & 1;
-    const int ql = blockIdx.x >> 1;
-    const int qg = p.q0 + ql;
+    // Persistent: CTAs [0, split0) work on d-part 0 of queries b, b + split0, ...; the rest on d-part 1.  The split
+    // follows the parts' cost (320 : 256 columns of reductions) so that both groups finish together.
+    const int part = static_cast<int>(blockIdx.x) >= p.split0;
+    const int q_first = part ? blockIdx.x - p.split0 : blockIdx.x;
+    const int q_stride = part ? gridDim.x - p.split0 : p.split0;
+    const int nq = p.nq;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n_blk = part ? 2 : 3;
@@ -641,12 +647,16 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         return;
     }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffMisc);
-    const uint32_t bar_sfull = smem_u32(bars);          // 1  S/dS tile landed
-    const uint32_t bar_sempty = bar_sfull + 8;          // 1  all UMMAs of the tile finished
-    const uint32_t bar_res = bar_sempty + 8;            // 1
-    const uint32_t bar_ufull = bar_res + 8;             // [kUnits]
+    const uint32_t bar_sfull = smem_u32(bars);          // 1  S tile landed
+    const uint32_t bar_sempty = bar_sfull + 8;          // 1  the tile's UMMAs on S finished
+    const uint32_t bar_dsfull = bar_sempty + 8;         // 1  dS tile landed
+    const uint32_t bar_dsempty = bar_dsfull + 8;        // 1  the tile's UMMAs on dS finished
+    const uint32_t bar_res = bar_dsempty + 8;           // 1  resident Q^T / dO^T of the current query landed
+    const uint32_t bar_resfree = bar_res + 8;           // 1  all UMMAs of the current query finished
+    const uint32_t bar_ufull = bar_resfree + 8;         // [kUnits]
     const uint32_t bar_uempty = bar_ufull + 8 * kUnits; // [kUnits]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (3 + 2 * kUnits));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (6 + 2 * kUnits));
+    static_assert(8 * (6 + 2 * kUnits) + 8 <= 128, "barrier area");
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const WaitCtx wc{p.g_err, s_abort};
 
@@ -654,7 +664,10 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         *s_abort = 0;
         mbar_init(bar_sfull, 1);
         mbar_init(bar_sempty, 1);
+        mbar_init(bar_dsfull, 1);
+        mbar_init(bar_dsempty, 1);
         mbar_init(bar_res, 1);
+        mbar_init(bar_resfree, 1);
         for (int i = 0; i < kUnits; ++i) {
             mbar_init(bar_ufull + 8 * i, 1);
             mbar_init(bar_uempty + 8 * i, 8);
@@ -682,49 +695,82 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tma_prefetch_desc(&tm_do);
             tma_prefetch_desc(&tm_s);
             tma_prefetch_desc(&tm_ds);
-            mbar_arrive_expect_tx(bar_res, (n_q + n_do) * C::kChunk);
-            const int row0 = qg * p.h_q;
             const uint64_t pol_stream = l2_policy_evict_first();
-            for (int j = 0; j < n_q; ++j)
-                tma_load_2d_hint(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * (chunk0 + j), row0, bar_res, pol_stream);
-            for (int j = 0; j < n_do; ++j)
-                tma_load_2d_hint(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res, pol_stream);
-            for (int tile = 0; tile < n_tiles; ++tile) {
-                mbar_wait(bar_sempty, (tile & 1) ^ 1, wc, kErrDkv + 1, kPollSleepNs);
-                mbar_arrive_expect_tx(bar_sfull, C::kStage);
-                const uint32_t dst = s_base + C::kOffStage;
-                // box = 128 keys of every head block -> [HP/8][128 keys][8 heads]
-                tma_load_4d_hint(dst, &tm_s, 0, tile * (kTileKeys / 32), 0, ql, bar_sfull, pol_stream);
-                tma_load_4d_hint(dst + C::kTileMat, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_sfull, pol_stream);
+            uint32_t gtile = 0, k = 0;
+            for (int ql = q_first; ql < nq; ql += q_stride, ++k) {
+                // the resident operands are replaced once the previous query's UMMAs are done; the drain warps
+                // meanwhile still work through the accumulator ring, so the reductions do not pause
+                if (k) mbar_wait(bar_resfree, (k - 1) & 1, wc, kErrDkv + 6, kPollSleepNs);
+                mbar_arrive_expect_tx(bar_res, (n_q + n_do) * C::kChunk);
+                const int row0 = (p.q0 + ql) * p.h_q;
+                for (int j = 0; j < n_q; ++j)
+                    tma_load_2d_hint(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * (chunk0 + j), row0, bar_res, pol_stream);
+                for (int j = 0; j < n_do; ++j)
+                    tma_load_2d_hint(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res, pol_stream);
+                for (int tile = 0; tile < n_tiles; ++tile, ++gtile) {
+                    // box = 128 keys of every head block -> [HP/8][128 keys][8 heads].  S and dS have a buffer and a
+                    // pair of barriers each: the next tile's S comes in while this tile's dS is being multiplied,
+                    // and the other way round.
+                    const uint32_t dst = s_base + C::kOffStage;
+                    mbar_wait(bar_sempty, (gtile & 1) ^ 1, wc, kErrDkv + 1, kPollSleepNs);
+                    mbar_arrive_expect_tx(bar_sfull, C::kTileMat);
+                    tma_load_4d_hint(dst, &tm_s, 0, tile * (kTileKeys / 32), 0, ql, bar_sfull, pol_stream);
+                    mbar_wait(bar_dsempty, (gtile & 1) ^ 1, wc, kErrDkv + 7, kPollSleepNs);
+                    mbar_arrive_expect_tx(bar_dsfull, C::kTileMat);
+                    tma_load_4d_hint(dst + C::kTileMat, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_dsfull, pol_stream);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_bf16(128, 128, 1, 0);  // A MN-major (d contiguous), B K-major
-            mbar_wait(bar_res, 0, wc, kErrDkv + 2);
             const uint32_t st_s = s_base + C::kOffStage;
             const uint32_t st_ds = st_s + C::kTileMat;
             int unit = 0;
-            for (int tile = 0; tile < n_tiles; ++tile) {
-                mbar_wait(bar_sfull, tile & 1, wc, kErrDkv + 4);
-                for (int blk = 0; blk < n_blk; ++blk, ++unit) {
-                    const int us = unit % kUnits;
-                    mbar_wait(bar_uempty + 8 * us, ((unit / kUnits) & 1) ^ 1, wc, kErrDkv + 3);
+            uint32_t gtile = 0, k = 0;
+            for (int ql = q_first; ql < nq; ql += q_stride, ++k) {
+            mbar_wait(bar_res, k & 1, wc, kErrDkv + 2);
+            for (int tile = 0; tile < n_tiles; ++tile, ++gtile) {
+                // pass 1: dO^T . S into the tile's accumulators (a free ring unit each); pass 2: += Q^T . dS
+                SMLA_STAMP(3, unit, 6);
+                mbar_wait(bar_sfull, gtile & 1, wc, kErrDkv + 4);
+                SMLA_STAMP(4, unit, 6);
+                for (int blk = 0; blk < n_blk; ++blk) {
+                    const int u = unit + blk, us = u % kUnits;
+                    SMLA_STAMP(0, u, 6);
+                    mbar_wait(bar_uempty + 8 * us, ((u / kUnits) & 1) ^ 1, wc, kErrDkv + 3);
+                    SMLA_STAMP(1, u, 6);
                     tc_fence_after_sync();
                     const uint32_t d = tmem + us * 128;
-                    const uint32_t a_do = s_base + C::kOffDO + 2 * blk * C::kChunk;
-                    const uint32_t a_q = s_base + C::kOffQ + 2 * blk * C::kChunk;
+                    // Part 0's third block has one real chunk (d 256..319).  On odd tiles it is placed in the upper
+                    // 64 rows of the block (the lower 64 repeat chunk 3 and are dropped), on even tiles in the lower
+                    // 64: the drain of that block then alternates between the two halves of the drain warps, i.e.
+                    // between the SM sub-partitions, whose reduction issue rate is what bounds this kernel.
+                    const int shift = (part == 0 && blk == 2 && (tile & 1) && !SMLA_DBG(64)) ? C::kChunk : 0;
+                    const uint32_t a_do = s_base + C::kOffDO + 2 * blk * C::kChunk - shift;
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
                                 make_smem_desc(st_s + ks * 4096, 2048, 128, kSwizzleNone), idesc, ks != 0);
+                    SMLA_STAMP(2, u, 6);
+                }
+                umma_commit(bar_sempty);
+                mbar_wait(bar_dsfull, gtile & 1, wc, kErrDkv + 8);
+                for (int blk = 0; blk < n_blk; ++blk) {
+                    const int us = (unit + blk) % kUnits;
+                    const uint32_t d = tmem + us * 128;
+                    const int shift = (part == 0 && blk == 2 && (tile & 1) && !SMLA_DBG(64)) ? C::kChunk : 0;
+                    const uint32_t a_q = s_base + C::kOffQ + 2 * blk * C::kChunk - shift;
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_q + ks * 2048, C::kChunk, 1024, kSwizzle128),
                                 make_smem_desc(st_ds + ks * 4096, 2048, 128, kSwizzleNone), idesc, 1);
                     umma_commit(bar_ufull + 8 * us);
                 }
-                umma_commit(bar_sempty);
+                umma_commit(bar_dsempty);
+                unit += n_blk;
+            }
+            umma_commit(bar_resfree);
             }
         }
     } else {
@@ -733,6 +779,8 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int d_part0 = chunk0 * 64;
         int* idx_s = reinterpret_cast<int*>(smem + C::kOffIdx) + (warp - 2) * 64;
         int unit = 0;
+        for (int ql = q_first; ql < nq; ql += q_stride) {
+        const int qg = p.q0 + ql;
         for (int tile = 0; tile < n_tiles; ++tile) {
             __syncwarp();
 #pragma unroll
@@ -744,31 +792,43 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             __syncwarp();
             for (int blk = 0; blk < n_blk; ++blk, ++unit) {
                 const int us = unit % kUnits;
+                if (threadIdx.x == 64) SMLA_STAMP(5, unit, 6);
                 mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
-                tc_fence_after_sync();
-                if (!(part == 0 && blk == 2 && quarter >= 2)) {   // padded rows are never drained
-                    float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane;
+                if (threadIdx.x == 64) SMLA_STAMP(6, unit, 6);
+                if (!SMLA_DBG(8)) tc_fence_after_sync();
+                const bool upper = part == 0 && blk == 2 && (tile & 1) && !SMLA_DBG(64);   // where the half block's real rows are
+                if (!(part == 0 && blk == 2 && (quarter >= 2) != upper)) {   // the other rows are never drained
+                    float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane - (upper ? 64 : 0);
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         uint32_t r[32];
-                        tmem_ld_32x32(taddr + 32 * i, r);
+                        if (!SMLA_DBG(2)) tmem_ld_32x32(taddr + 32 * i, r);
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) r[j] = 0x3a000000u + j + unit;
+                        }
                         int ix[32];
 #pragma unroll
                         for (int v = 0; v < 8; ++v) {
-                            const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
+                            int4 t;
+                            if (!SMLA_DBG(4)) t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
+                            else t = make_int4((unit * 61 + v * 4) & 8191, (unit * 61 + v * 4 + 1) & 8191, (unit * 61 + v * 4 + 2) & 8191, (unit * 61 + v * 4 + 3) & 8191);
                             ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
                         }
-                        tmem_ld_wait();
+                        if (!SMLA_DBG(32)) tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (ix[j] >= 0) red_add_f32(out + static_cast<size_t>(ix[j]) * kDQK, __uint_as_float(r[j]));
+                            red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r[j]),
+                                               (SMLA_DBG(1) && r[j] != 0x12345u) ? -1 : ix[j]);
                     }
                 }
-                tc_fence_before_sync();
+                if (!SMLA_DBG(16)) tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_uempty + 8 * us);
+                if (threadIdx.x == 64) SMLA_STAMP(7, unit, 6);
             }
+        }
         }
     }
     tc_fence_before_sync();
