@@ -269,6 +269,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             split_grid(nq, 320, 256, &grid, &kp.split0);     // reductions into 320 and 256 columns of dKV
 #ifdef SMLA_TRACE
             if (getenv("SMLA_SPLIT0")) kp.split0 = atoi(getenv("SMLA_SPLIT0"));
+            if (getenv("SMLA_GRID")) grid = atoi(getenv("SMLA_GRID"));
 #endif
             smla_dkv_kernel<HP><<<grid, dk::kThreads, dk::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s128, tm_ds128, kp);
             ++g_last_launches;

@@ -178,7 +178,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const uint32_t s_base = smem_u32(smem);
     uint8_t* misc = smem + C::kOffMisc;
     float* lse_s = reinterpret_cast<float*>(misc);          // [HP] base-2 lse, +inf for padded heads
-    float* delta_s = lse_s + HP;                            // [HP]
+    float* delta_s = lse_s + HP;                            // [HP] Delta * sm_scale
     uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 1024);
     const uint32_t bar_full = smem_u32(bars);               // [kStages] gathered chunk landed (even CTA: in both CTAs)
     const uint32_t bar_empty = bar_full + 8 * kStages;      // [kStages] pair UMMAs reading the slot finished
@@ -421,7 +421,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             if (t >= 2 * HP) return 0.f;
             if (h >= p.h_q) return t < HP ? __int_as_float(0x7f800000) : 0.f;
             const size_t o = static_cast<size_t>(p.q0 + ql) * p.h_q + h;
-            return t < HP ? p.lse[o] * p.lse_mult : p.delta[o];
+            return t < HP ? p.lse[o] * p.lse_mult : p.delta[o] * p.sm_scale;
         };
         float stat_next = load_stat(pair);
         int gt = 0;
@@ -468,6 +468,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     const size_t off = static_cast<size_t>(ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
                     __nv_bfloat16* s_out = p.s_scr + off;
                     __nv_bfloat16* ds_out = p.ds_scr + off;
+                    const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
 #pragma unroll 1
                     for (int c0 = 0; c0 < (SMLA_DBG(2) ? 0 : NH); c0 += 16) {
                         uint32_t pv[16], dpv[16];
@@ -485,14 +486,17 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int c = 4 * v + e;
-                                const float sx = valid ? ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e])) : 0.f;
+                                // dv holds Delta * sm_scale: dS = S * (dP - Delta) * sm_scale in two instructions
+                                const float sx = ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e]));
                                 sv[e] = sx;
-                                dsv[e] = valid ? sx * (__uint_as_float(dpv[c]) - dv[e]) * p.sm_scale : 0.f;
+                                dsv[e] = sx * fmaf(__uint_as_float(dpv[c]), p.sm_scale, -dv[e]);
                             }
-                            so[2 * v] = pack_bf16x2(sv[0], sv[1]);
-                            so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]);
-                            dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]);
-                            dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]);
+                            // an unused slot is masked after packing (one AND per two values; also wipes the
+                            // NaN / inf its never-gathered operand row may have produced)
+                            so[2 * v] = pack_bf16x2(sv[0], sv[1]) & vmask;
+                            so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]) & vmask;
+                            dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]) & vmask;
+                            dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]) & vmask;
                         }
                         if (!SMLA_DBG(1) || so[0] == 0x12345679u) {
                             // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
@@ -837,13 +841,18 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // =============================================================================================
-// dq: one CTA per (query, d-part); same d split as dkv; 13 warps.
-//   warps 0-3   epilogue: TMEM -> bf16 -> dQ[q, head, d]
+// dq: one CTA per (query, d-part); same d split as dkv; 14 warps.
+//   warps 0-3   epilogue: TMEM -> bf16 -> dQ[q, head, d]; lane = head, so a thread stores whole 64-byte pieces of
+//               its head's row
 //   warps 4-11  producers: per 64-key tile the part's columns of the kv rows picked by index (16-byte
 //               cp.async into the swizzled layout)
-//   warp 13     TMA: the dS scratch tile, and the first two column chunks of the tile through gather4
-//   warp 12     UMMA issuer: acc[blk][128 d, HP heads] += Kg^T . dS^T  (both operands MN-major:
-//               the key index is the contraction and runs along shared-memory rows)
+//   warp 13     TMA: the dS scratch tile
+//   warp 12     UMMA issuer: acc[128 heads, d of the part] += dS^T . Kg  (both operands MN-major: the key index is
+//               the contraction and runs along shared-memory rows).  Heads are the M side so that N can be 256
+//               columns of d: a 128x256x16 UMMA reads 12 KB of shared memory per 128 cycles of math, whereas the
+//               transposed 128x128x16 form reads 8 KB per 64 cycles, which is all the bandwidth there is (measured
+//               ~100 cycles per UMMA instead of 64).  With HP = 64 the upper 64 accumulator rows are computed from
+//               whatever follows the dS tile in shared memory and never read.
 // =============================================================================================
 namespace dq {
 constexpr int kThreads = 448;
@@ -854,10 +863,11 @@ constexpr int kTmaChunks = 0;   // column chunks of a tile routed through TMA ga
 template <int HP> struct Cfg {
     static constexpr int kKgBytes = 5 * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
-    static constexpr int kStage = kKgBytes + kDsBytes;     // dS right after Kg: block 2's padded rows read dS
+    static constexpr int kStage = kKgBytes + kDsBytes;     // dS right after Kg
     static constexpr int kOffMisc = kStages * kStage;
-    static constexpr int kSmemBytes = kOffMisc + 256 + 1024;
-    static constexpr int kTmemCols = HP == 128 ? 512 : 256;
+    // the A operand always spans 128 heads: with HP = 64 its upper half reads 8 KB past the dS tile
+    static constexpr int kSmemBytes = kOffMisc + 256 + 1024 + (HP == 64 ? 8192 : 0);
+    static constexpr int kTmemCols = 512;                  // up to 320 columns of d used
 };
 }  // namespace dq
 
@@ -874,8 +884,6 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     // d-part 0 gathers kv column chunks [0, kSplit), part 1 [kSplit, kTotal): (5, 9) for dQ, (4, 8) for o = S.V
     const int chunk0 = part ? kSplit : 0;
     const int n_ch = part ? kTotal - kSplit : kSplit;
-    const int n_blk = (n_ch + 1) >> 1;
-    const bool half_last = n_ch & 1;      // last block has 64 real rows
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -906,6 +914,9 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
+#ifdef SMLA_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == p.trace_cta) p.trace[504] = clock64();
+#endif
 
     if (warp >= 4 && warp < 12) {
         const int pt = threadIdx.x - 128;   // 0..255
@@ -927,8 +938,10 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                 src[i] = kvb + static_cast<size_t>(in_range ? idx : 0) * (kDQK * 2);
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);
+            if (pt == 0) SMLA_STAMP(3, tile, 4);
             const uint32_t d = dst0 + s * C::kStage;
             for (int c = kTmaChunks; c < n_ch; ++c) {
+                if (SMLA_DBG(4)) continue;
                 cp_async16_zfill_hint(d + c * 8192, src[0] + c * 128, nb[0], pol_keep);
                 cp_async16_zfill_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, nb[1], pol_keep);
             }
@@ -952,6 +965,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                 }
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4, kPollSleepNs);
+            if (lane == 0) SMLA_STAMP(4, tile, 4);
             const uint32_t dst = s_base + s * C::kStage;
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
@@ -967,58 +981,71 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         }
     } else if (warp == 12) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(128, HP, 1, 1);
+            // N = up to four column chunks (256 d) in one UMMA, the rest (one chunk) in a second
+            const int n1 = (n_ch < 4 ? n_ch : 4) * 64, n2 = (n_ch - 4) * 64;
+            const uint32_t idesc1 = make_idesc_bf16(128, n1, 1, 1);
+            const uint32_t idesc2 = make_idesc_bf16(128, n2 > 0 ? n2 : 64, 1, 1);
             for (int tile = 0; tile < n_tiles; ++tile) {
                 const int s = tile % kStages;
+                SMLA_STAMP(0, tile, 4);
                 mbar_wait(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
+                SMLA_STAMP(1, tile, 4);
                 fence_proxy_async_smem();
                 tc_fence_after_sync();
                 const uint32_t kg = s_base + s * C::kStage;
                 const uint32_t ds = kg + C::kKgBytes;
-                for (int blk = 0; blk < n_blk; ++blk) {
+                if (!SMLA_DBG(8)) {
 #pragma unroll
-                    for (int ks = 0; ks < kTileKeys / 16; ++ks)
-                        umma_ss(tmem + blk * HP, make_smem_desc(kg + 2 * blk * 8192 + ks * 2048, 8192, 1024, kSwizzle128),
-                                make_smem_desc(ds + ks * 256, 128, 1024, kSwizzleNone), idesc, (tile | ks) != 0);
+                for (int ks = 0; ks < kTileKeys / 16; ++ks) {
+                    // A = dS^T: [HP/8 head blocks][64 keys][8 heads], 8-key groups 128 B apart, head blocks 1 KB apart
+                    const uint64_t a = make_smem_desc(ds + ks * 256, 128, 1024, kSwizzleNone);
+                    umma_ss(tmem, a, make_smem_desc(kg + ks * 2048, 8192, 1024, kSwizzle128), idesc1, (tile | ks) != 0);
+                    if (n2 > 0)
+                        umma_ss(tmem + 256, a, make_smem_desc(kg + 4 * 8192 + ks * 2048, 8192, 1024, kSwizzle128), idesc2,
+                                (tile | ks) != 0);
+                }
                 }
                 umma_commit(bar_empty + 8 * s);
+                SMLA_STAMP(2, tile, 4);
             }
             umma_commit(bar_acc);
         }
     } else {
         const int quarter = warp;
         mbar_wait(bar_acc, 0, wc, kErrDq + 3, kPollSleepNs);
+        if (threadIdx.x == 0) SMLA_STAMP(6, 4, 4);
         tc_fence_after_sync();
-        // The accumulator has d on the lanes and heads on the columns; the output wants rows of d per head.
-        // Transpose a block through shared memory (the pipeline stages are idle by now) so that the global
-        // stores are 16-byte vectors instead of 2-byte scalars.
+        // lane = head, columns = d of the part.  Each thread converts its head's row to bf16 in shared memory (the
+        // pipeline stages are idle by now; rows 16 bytes apart modulo 128 so that the 16-byte stores of a warp
+        // spread over all banks) and sends it off as one bulk copy: whole cache lines instead of 32 scattered
+        // 16-byte pieces per store instruction.
         constexpr int kPitch = kTotal * 64;      // 576 for dQ, 512 for o
-        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);     // [HP heads][128 d]
-        const int tid = threadIdx.x;             // 0..127
-        for (int blk = 0; blk < n_blk; ++blk) {
-            const int d_real = (half_last && blk == n_blk - 1) ? 64 : 128;
-            if (quarter * 32 < d_real) {
-                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + blk * HP;
+        constexpr int kRowBytes = 5 * 128 + 16;  // up to five column chunks per part
+        const int head = quarter * 32 + lane;
+        const uint32_t row_s = s_base + head * kRowBytes;
+        if (quarter * 32 < p.h_q) {               // warp-uniform: heads are padded to a multiple of 8 only
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-                for (int cb = 0; cb < HP / 32; ++cb) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + cb * 32, r);
-                    tmem_ld_wait();
+            for (int cg = 0; cg < n_ch * 2; ++cg) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + cg * 32, r);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        stg[(cb * 32 + j) * 128 + quarter * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                }
+                for (int v = 0; v < 4; ++v)
+                    st_shared_v4(row_s + cg * 64 + v * 16,
+                                 pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1])),
+                                 pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                                 pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                                 pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
             }
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-            const int upr_log2 = d_real == 128 ? 4 : 3;      // 16 or 8 sixteen-byte units per head row
-            __nv_bfloat16* out = p.gout + static_cast<size_t>(qg) * p.h_q * kPitch + chunk0 * 64 + blk * 128;
-            for (int u = tid; u < (p.h_q << upr_log2); u += 128) {
-                const int h = u >> upr_log2, c = u & ((1 << upr_log2) - 1);
-                const uint4 v = *reinterpret_cast<const uint4*>(stg + h * 128 + c * 8);
-                *reinterpret_cast<uint4*>(out + static_cast<size_t>(h) * kPitch + c * 8) = v;
+            if (head < p.h_q) {
+                fence_proxy_async_smem();         // this thread's row only: no one else touches it
+                bulk_store(p.gout + (static_cast<size_t>(qg) * p.h_q + head) * kPitch + chunk0 * 64, row_s, n_ch * 128);
+                bulk_commit();
+                bulk_wait_read();
             }
-            asm volatile("bar.sync 2, 128;" ::: "memory");
         }
+        if (threadIdx.x == 0) SMLA_STAMP(7, 4, 4);
     }
     tc_fence_before_sync();
     __syncthreads();
