@@ -242,11 +242,6 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     kp.lse_mult = p->lse_is_base2 ? 1.0f : 1.4426950408889634f;
     kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
     kp.q_start = kp.causal ? p->q_start_index_s : 0;
-#ifdef SMLA_TRACE
-    kp.trace = reinterpret_cast<long long*>(ws + pl.delta_off) ;   // development builds: stamps overwrite Delta[0..512)
-    kp.trace_cta = getenv("SMLA_TRACE_CTA") ? atoi(getenv("SMLA_TRACE_CTA")) : 0;
-    kp.dbg = getenv("SMLA_DBG") ? atoi(getenv("SMLA_DBG")) : 0;
-#endif
 
     if (stages & SMLA_STAGE_DELTA) {
         const int n_rows = p->s_q * p->h_q;
@@ -267,10 +262,6 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
         if (stages & SMLA_STAGE_DKV) {
             int grid = 0;
             split_grid(nq, 320, 256, &grid, &kp.split0);     // reductions into 320 and 256 columns of dKV
-#ifdef SMLA_TRACE
-            if (getenv("SMLA_SPLIT0")) kp.split0 = atoi(getenv("SMLA_SPLIT0"));
-            if (getenv("SMLA_GRID")) grid = atoi(getenv("SMLA_GRID"));
-#endif
             smla_dkv_kernel<HP><<<grid, dk::kThreads, dk::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s128, tm_ds128, kp);
             ++g_last_launches;
         }

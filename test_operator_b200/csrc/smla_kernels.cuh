@@ -52,11 +52,6 @@ struct KParams {
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
-#ifdef SMLA_TRACE
-    long long* trace;         // development builds only: cycle stamps of CTA `trace_cta`
-    int trace_cta;
-    int dbg;                  // development builds only: switches parts of a kernel off for timing experiments
-#endif
 };
 
 // S / dS scratch of one query: [HP/8 head blocks][topk_pad keys][8 heads] bf16, i.e. the UMMA core matrices
@@ -67,14 +62,6 @@ __device__ __forceinline__ size_t scratch_offset(int key, int head, int topk_pad
     return (static_cast<size_t>(head >> 3) * topk_pad + key) * 8 + (head & 7);
 }
 
-#ifdef SMLA_TRACE
-// stamp event `ev` (0..7) of step `i`, steps [lo, lo+64)
-#define SMLA_STAMP(ev, i, lo) do { if (blockIdx.x == p.trace_cta && (i) >= (lo) && (i) < (lo) + 64) p.trace[((i) - (lo)) * 8 + (ev)] = clock64(); } while (0)
-#define SMLA_DBG(bit) ((p.dbg & (bit)) != 0)
-#else
-#define SMLA_STAMP(ev, i, lo) do { } while (0)
-#define SMLA_DBG(bit) false
-#endif
 
 // error codes recorded by bounded waits: 100*kernel + site
 enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300 };
@@ -197,7 +184,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         tmem_slot[2] = 0;
         for (int i = 0; i < kStages; ++i) {
             // the even CTA's "full" also counts one arrival forwarded from the odd CTA
-            mbar_init(bar_full + 8 * i, (SMLA_DBG(16) ? 8 : kProducerThreads) + (rank == 0 ? 1 : 0));
+            mbar_init(bar_full + 8 * i, kProducerThreads + (rank == 0 ? 1 : 0));
             mbar_init(bar_empty + 8 * i, 1);
         }
         for (int i = 0; i < kQChunks; ++i) {
@@ -226,14 +213,6 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
     const int nq = p.nq;
-#ifdef SMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x == p.trace_cta) {
-        unsigned long long gtime;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gtime));
-        p.trace[504] = clock64();
-        p.trace[505] = static_cast<long long>(gtime);
-    }
-#endif
 
     if (warp >= 8 && warp < 16) {
         // ------------------------------------------------------------------ gather producers
@@ -273,22 +252,11 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 if (tile + 1 < n_tiles) load_idx(ql, tile + 1, idx_next);
                 else load_idx(ql + n_pairs, 0, idx_next);
                 for (int j = 0; j < kQChunks; ++j) {
-                    if (SMLA_DBG(2048)) {
-                        if (lane == 0) mbar_wait(bar_empty + 8 * s, ph, wc, kErrRecompute + 11, kPollSleepNs);
-                        __syncwarp();
-                    } else
                     mbar_wait(bar_empty + 8 * s, ph, wc, kErrRecompute + 11, kPollSleepNs);
-#ifdef SMLA_TRACE
-                    if (pt == 0 && ql == pair) SMLA_STAMP(0, tile * kQChunks + j, 18);
-                    if (pt == 255 && ql == pair) SMLA_STAMP(1, tile * kQChunks + j, 18);
-#endif
                     const uint32_t d = dst0 + s * kChunkA;
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        if (!SMLA_DBG(4)) cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
-                    if (SMLA_DBG(16)) {
-                        if (lane == 0) mbar_arrive(bar_full + 8 * s);
-                    } else
+                        cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
                     cp_async_mbar_arrive_noinc(bar_full + 8 * s);
                     if (++s == kStages) {
                         s = 0;
@@ -367,24 +335,18 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     const int b = gt & 1;
                     if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gt >> 1) & 1) ^ 1, wc, kErrRecompute + 13);
                     if (tile == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrRecompute + 12);
-                    if (x == 0) SMLA_STAMP(2, it, 18);
                     mbar_spin(bar_full + 8 * s, ph, wc, kErrRecompute + 14);
-                    if (x == 0) SMLA_STAMP(3, it, 18);
                     flag_wait(tok, static_cast<uint32_t>(it), wc, kErrRecompute + 19);
                     tc_fence_after_sync();
-                    if (x == 0) SMLA_STAMP(4, it, 18);
                     const uint32_t d = tmem + b * C::kAccCols;
                     const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
                     const uint32_t b_lo = b_lo0 + j * (C::kBChunk >> 4);
-                    if (!SMLA_DBG(8)) {
                     umma_ss_2cta(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
 #pragma unroll
                     for (int kk = 1; kk < 4; ++kk)   // 32 bytes further along K = +2 in the address field
                         umma_ss_2cta(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
-                    }
                     tc_fence_before_sync();
                     flag_store(tok, static_cast<uint32_t>(it + 1));
-                    if (x == 0) SMLA_STAMP(5, it, 18);
                     umma_commit_2cta_mask(bar_empty + 8 * s, 3);
                     if (tile == n_tiles - 1) umma_commit_2cta_mask(bar_bfree + 8 * j, 3);   // the next query's chunk may come in
                     if (j == kQChunks - 1) umma_commit_2cta_mask(bar_tfull + 8 * b, 3);
@@ -439,7 +401,6 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const bool valid = slot_valid(idx, qg, p);
                 const int b = gt & 1;
                 mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
-                if (threadIdx.x == 0) SMLA_STAMP(6, gt * kQChunks, 18);
                 tc_fence_after_sync();
                 if constexpr (kFwd) {
                     const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
@@ -451,7 +412,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     for (int c0 = 0; c0 < NH; c0 += 16) {
                         uint32_t pv[16];
                         tmem_ld_32x16(taddr + c0, pv);
-                        if (!SMLA_DBG(32)) tmem_ld_wait();
+                        tmem_ld_wait();
                         uint32_t lo[8], hi[8];
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
@@ -470,11 +431,11 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     __nv_bfloat16* ds_out = p.ds_scr + off;
                     const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < (SMLA_DBG(2) ? 0 : NH); c0 += 16) {
+                    for (int c0 = 0; c0 < NH; c0 += 16) {
                         uint32_t pv[16], dpv[16];
                         tmem_ld_32x16(taddr + c0, pv);
                         tmem_ld_32x16(taddr + NH + c0, dpv);
-                        if (!SMLA_DBG(32)) tmem_ld_wait();
+                        tmem_ld_wait();
                         uint32_t so[8], dso[8];
                         const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
                         const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
@@ -498,7 +459,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                             dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]) & vmask;
                             dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]) & vmask;
                         }
-                        if (!SMLA_DBG(1) || so[0] == 0x12345679u) {
+                        {
                             // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
                             __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
                             __nv_bfloat16* d0 = ds_out + static_cast<size_t>(c0) * p.topk_pad;
@@ -512,21 +473,15 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
-                if (threadIdx.x == 0) SMLA_STAMP(7, gt * kQChunks, 18);
+                // The accumulator reads have completed (tcgen05.wait::ld above), which is all the issuer needs to know;
+                // the stores to the scratch are ordered by the kernel boundary.  A cluster-scope release here would hold
+                // the warp for about a thousand cycles per tile.
+                if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * b);
             }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-#ifdef SMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x == p.trace_cta) {
-        unsigned long long gtime;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gtime));
-        p.trace[506] = clock64();
-        p.trace[507] = static_cast<long long>(gtime);
-    }
-#endif
     cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
     if (warp == 16) tmem_dealloc_2cta(tmem, C::kTmemCols);
 }
@@ -736,34 +691,29 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_wait(bar_res, k & 1, wc, kErrDkv + 2);
             for (int tile = 0; tile < n_tiles; ++tile, ++gtile) {
                 // pass 1: dO^T . S into the tile's accumulators (a free ring unit each); pass 2: += Q^T . dS
-                SMLA_STAMP(3, unit, 6);
                 mbar_wait(bar_sfull, gtile & 1, wc, kErrDkv + 4);
-                SMLA_STAMP(4, unit, 6);
                 for (int blk = 0; blk < n_blk; ++blk) {
                     const int u = unit + blk, us = u % kUnits;
-                    SMLA_STAMP(0, u, 6);
                     mbar_wait(bar_uempty + 8 * us, ((u / kUnits) & 1) ^ 1, wc, kErrDkv + 3);
-                    SMLA_STAMP(1, u, 6);
                     tc_fence_after_sync();
                     const uint32_t d = tmem + us * 128;
                     // Part 0's third block has one real chunk (d 256..319).  On odd tiles it is placed in the upper
                     // 64 rows of the block (the lower 64 repeat chunk 3 and are dropped), on even tiles in the lower
                     // 64: the drain of that block then alternates between the two halves of the drain warps, i.e.
                     // between the SM sub-partitions, whose reduction issue rate is what bounds this kernel.
-                    const int shift = (part == 0 && blk == 2 && (tile & 1) && !SMLA_DBG(64)) ? C::kChunk : 0;
+                    const int shift = (part == 0 && blk == 2 && (tile & 1)) ? C::kChunk : 0;
                     const uint32_t a_do = s_base + C::kOffDO + 2 * blk * C::kChunk - shift;
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
                         umma_ss(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
                                 make_smem_desc(st_s + ks * 4096, 2048, 128, kSwizzleNone), idesc, ks != 0);
-                    SMLA_STAMP(2, u, 6);
                 }
                 umma_commit(bar_sempty);
                 mbar_wait(bar_dsfull, gtile & 1, wc, kErrDkv + 8);
                 for (int blk = 0; blk < n_blk; ++blk) {
                     const int us = (unit + blk) % kUnits;
                     const uint32_t d = tmem + us * 128;
-                    const int shift = (part == 0 && blk == 2 && (tile & 1) && !SMLA_DBG(64)) ? C::kChunk : 0;
+                    const int shift = (part == 0 && blk == 2 && (tile & 1)) ? C::kChunk : 0;
                     const uint32_t a_q = s_base + C::kOffQ + 2 * blk * C::kChunk - shift;
 #pragma unroll
                     for (int ks = 0; ks < HP / 16; ++ks)
@@ -796,41 +746,41 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             __syncwarp();
             for (int blk = 0; blk < n_blk; ++blk, ++unit) {
                 const int us = unit % kUnits;
-                if (threadIdx.x == 64) SMLA_STAMP(5, unit, 6);
                 mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
-                if (threadIdx.x == 64) SMLA_STAMP(6, unit, 6);
-                if (!SMLA_DBG(8)) tc_fence_after_sync();
-                const bool upper = part == 0 && blk == 2 && (tile & 1) && !SMLA_DBG(64);   // where the half block's real rows are
+                tc_fence_after_sync();
+                const bool upper = part == 0 && blk == 2 && (tile & 1);   // where the half block's real rows are
                 if (!(part == 0 && blk == 2 && (quarter >= 2) != upper)) {   // the other rows are never drained
                     float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane - (upper ? 64 : 0);
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        uint32_t r[32];
-                        if (!SMLA_DBG(2)) tmem_ld_32x32(taddr + 32 * i, r);
-                        else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) r[j] = 0x3a000000u + j + unit;
-                        }
-                        int ix[32];
+                    // two halves of 32 keys; the second half's accumulator load is in flight while the first half's
+                    // reductions are issued
+                    uint32_t r0[32], r1[32];
+                    int ix[32];
+                    auto load_ix = [&](int i) {
 #pragma unroll
                         for (int v = 0; v < 8; ++v) {
-                            int4 t;
-                            if (!SMLA_DBG(4)) t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
-                            else t = make_int4((unit * 61 + v * 4) & 8191, (unit * 61 + v * 4 + 1) & 8191, (unit * 61 + v * 4 + 2) & 8191, (unit * 61 + v * 4 + 3) & 8191);
+                            const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
                             ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
                         }
-                        if (!SMLA_DBG(32)) tmem_ld_wait();
+                    };
+                    tmem_ld_32x32(taddr, r0);
+                    load_ix(0);
+                    tmem_ld_wait();
+                    tmem_ld_32x32(taddr + 32, r1);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r[j]),
-                                               (SMLA_DBG(1) && r[j] != 0x12345u) ? -1 : ix[j]);
-                    }
+                    for (int j = 0; j < 32; ++j)
+                        red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r0[j]),
+                                           ix[j]);
+                    load_ix(1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r1[j]),
+                                           ix[j]);
                 }
-                if (!SMLA_DBG(16)) tc_fence_before_sync();
+                tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_uempty + 8 * us);
-                if (threadIdx.x == 64) SMLA_STAMP(7, unit, 6);
             }
         }
         }
@@ -914,9 +864,6 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
-#ifdef SMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x == p.trace_cta) p.trace[504] = clock64();
-#endif
 
     if (warp >= 4 && warp < 12) {
         const int pt = threadIdx.x - 128;   // 0..255
@@ -938,10 +885,8 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                 src[i] = kvb + static_cast<size_t>(in_range ? idx : 0) * (kDQK * 2);
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);
-            if (pt == 0) SMLA_STAMP(3, tile, 4);
             const uint32_t d = dst0 + s * C::kStage;
             for (int c = kTmaChunks; c < n_ch; ++c) {
-                if (SMLA_DBG(4)) continue;
                 cp_async16_zfill_hint(d + c * 8192, src[0] + c * 128, nb[0], pol_keep);
                 cp_async16_zfill_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, nb[1], pol_keep);
             }
@@ -965,7 +910,6 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                 }
             }
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4, kPollSleepNs);
-            if (lane == 0) SMLA_STAMP(4, tile, 4);
             const uint32_t dst = s_base + s * C::kStage;
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
@@ -987,14 +931,11 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
             const uint32_t idesc2 = make_idesc_bf16(128, n2 > 0 ? n2 : 64, 1, 1);
             for (int tile = 0; tile < n_tiles; ++tile) {
                 const int s = tile % kStages;
-                SMLA_STAMP(0, tile, 4);
                 mbar_wait(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
-                SMLA_STAMP(1, tile, 4);
                 fence_proxy_async_smem();
                 tc_fence_after_sync();
                 const uint32_t kg = s_base + s * C::kStage;
                 const uint32_t ds = kg + C::kKgBytes;
-                if (!SMLA_DBG(8)) {
 #pragma unroll
                 for (int ks = 0; ks < kTileKeys / 16; ++ks) {
                     // A = dS^T: [HP/8 head blocks][64 keys][8 heads], 8-key groups 128 B apart, head blocks 1 KB apart
@@ -1004,16 +945,13 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                         umma_ss(tmem + 256, a, make_smem_desc(kg + 4 * 8192 + ks * 2048, 8192, 1024, kSwizzle128), idesc2,
                                 (tile | ks) != 0);
                 }
-                }
                 umma_commit(bar_empty + 8 * s);
-                SMLA_STAMP(2, tile, 4);
             }
             umma_commit(bar_acc);
         }
     } else {
         const int quarter = warp;
         mbar_wait(bar_acc, 0, wc, kErrDq + 3, kPollSleepNs);
-        if (threadIdx.x == 0) SMLA_STAMP(6, 4, 4);
         tc_fence_after_sync();
         // lane = head, columns = d of the part.  Each thread converts its head's row to bf16 in shared memory (the
         // pipeline stages are idle by now; rows 16 bytes apart modulo 128 so that the 16-byte stores of a warp
@@ -1045,7 +983,6 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
                 bulk_wait_read();
             }
         }
-        if (threadIdx.x == 0) SMLA_STAMP(7, 4, 4);
     }
     tc_fence_before_sync();
     __syncthreads();
