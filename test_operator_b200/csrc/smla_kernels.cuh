@@ -556,13 +556,13 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
 //              [128 keys x HP heads] (B operand, K-major); one shared-memory stage
 //   warp 1     UMMA issuer: unit = (tile, block of 128 d rows): acc[128 d, 128 keys] = dO^T . S + Q^T . dS
 //              into a ring of four 128-column TMEM units, so the MMAs run ahead of the drain
-//   warps 2-9  drain: thread = d row, each warp owns 32 d rows x 64 keys of a unit; one fp32 reduction
-//              per key, 32 lanes -> 128 contiguous bytes of dKV
+//   warps 2-17 drain, two groups of eight taking alternate units: thread = d row, each warp owns 32 d rows x 64 keys
+//              of a unit; one fp32 reduction per key, 32 lanes -> 128 contiguous bytes of dKV
 // Part 0's third block has 64 real rows (d 256..319); its other 64 rows read a neighbouring chunk
 // and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
 // =============================================================================================
 namespace dk {
-constexpr int kThreads = 320;   // warp 0 producer, warp 1 UMMA issuer, warps 2-9 drain
+constexpr int kThreads = 576;   // warp 0 producer, warp 1 UMMA issuer, warps 2-17 drain (two groups of eight)
 constexpr int kTileKeys = 128;
 constexpr int kResChunks = 5;
 constexpr int kUnits = 4;       // TMEM accumulator ring: 4 x 128 columns
@@ -574,7 +574,7 @@ template <int HP> struct Cfg {
     static constexpr int kOffDO = kResChunks * kChunk;
     static constexpr int kOffStage = 2 * kResChunks * kChunk;
     static constexpr int kOffMisc = kOffStage + kStage;
-    static constexpr int kOffIdx = kOffMisc + 128;          // 8 drain warps x 64 int
+    static constexpr int kOffIdx = kOffMisc + 128;          // [2 groups][2 tile parities][2 key halves][64] int
     static constexpr int kSmemBytes = kOffMisc + 128 + 2048 + 896;   // all of the 227 KB; 896 B alignment slack
 };
 }  // namespace dk
@@ -728,60 +728,79 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
         }
     } else {
-        const int quarter = warp & 3;
-        const int e = (warp - 2) >> 2;          // which 64 keys of the 128-key tile this warp scatters
+        // Two groups of eight drain warps take alternate accumulator units.  A unit costs a warp a fixed part (wait for
+        // the UMMAs, accumulator load, indices: ~1.4k cycles) and the issue of 64 reductions (~1.8k cycles at the SM's
+        // reduction rate); with one group the two add up, with two groups one group's fixed part runs under the other
+        // group's reductions.
+        const int dw = warp - 2;                // 0..15
+        const int grp = dw >> 3;
+        const int quarter = warp & 3;           // the TMEM lane quarter a warp may read is warp % 4
+        const int e = (dw >> 2) & 1;            // which 64 keys of the 128-key tile this warp scatters
+        const int member = dw & 3;              // the four warps of a (group, key half) share one index buffer
         const int d_part0 = chunk0 * 64;
-        int* idx_s = reinterpret_cast<int*>(smem + C::kOffIdx) + (warp - 2) * 64;
-        int unit = 0;
-        for (int ql = q_first; ql < nq; ql += q_stride) {
-        const int qg = p.q0 + ql;
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            __syncwarp();
+        const int upq = n_tiles * n_blk;        // units per query: even, because top-k is padded to 256 keys
+        // index buffers [group][tile parity][key half][64]: filled by member 0 from registers it loaded one tile ahead,
+        // published with a named barrier of the four warps.  Every tile shows up in both groups' unit sequences and
+        // the barrier keeps the four within one tile of each other, so two buffers per (group, key half) suffice.
+        int* idx_base = reinterpret_cast<int*>(smem + C::kOffIdx) + (grp * 4 + e) * 64;
+        const int bar_id = 1 + grp * 2 + e;
+        int pf[2] = {-1, -1};
+        auto fetch_idx = [&](int ql, int tile) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int key = tile * kTileKeys + 64 * e + 32 * i + lane;
-                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                idx_s[32 * i + lane] = slot_valid(idx, qg, p) ? idx : -1;
+                const int qg = p.q0 + ql;
+                const int idx = (ql < nq && key < p.topk) ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                pf[i] = (ql < nq && slot_valid(idx, qg, p)) ? idx : -1;
             }
-            __syncwarp();
-            for (int blk = 0; blk < n_blk; ++blk, ++unit) {
-                const int us = unit % kUnits;
-                mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
-                tc_fence_after_sync();
-                const bool upper = part == 0 && blk == 2 && (tile & 1);   // where the half block's real rows are
-                if (!(part == 0 && blk == 2 && (quarter >= 2) != upper)) {   // the other rows are never drained
-                    float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane - (upper ? 64 : 0);
-                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
-                    // two halves of 32 keys; the second half's accumulator load is in flight while the first half's
-                    // reductions are issued
-                    uint32_t r0[32], r1[32];
+        };
+        if (member == 0) fetch_idx(q_first, 0);
+        uint32_t qn = 0;
+        for (int ql = q_first; ql < nq; ql += q_stride, ++qn) {
+        int last_tile = -1;
+        for (int ul = grp; ul < upq; ul += 2) {
+            const int tile = ul / n_blk, blk = ul - tile * n_blk;
+            const uint32_t unit = qn * upq + ul;
+            const int us = unit % kUnits;
+            int* idx_s = idx_base + (tile & 1) * 128;
+            if (tile != last_tile) {
+                last_tile = tile;
+                if (member == 0) {
+                    idx_s[lane] = pf[0];
+                    idx_s[32 + lane] = pf[1];
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                if (member == 0) {
+                    if (tile + 1 < n_tiles) fetch_idx(ql, tile + 1);
+                    else fetch_idx(ql + q_stride, 0);
+                }
+            }
+            mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
+            tc_fence_after_sync();
+            const bool upper = part == 0 && blk == 2 && (tile & 1);   // where the half block's real rows are
+            if (!(part == 0 && blk == 2 && (quarter >= 2) != upper)) {   // the other rows are never drained
+                float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane - (upper ? 64 : 0);
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + 32 * i, r);
                     int ix[32];
-                    auto load_ix = [&](int i) {
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
-                            ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
-                        }
-                    };
-                    tmem_ld_32x32(taddr, r0);
-                    load_ix(0);
-                    tmem_ld_wait();
-                    tmem_ld_32x32(taddr + 32, r1);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r0[j]),
-                                           ix[j]);
-                    load_ix(1);
+                    for (int v = 0; v < 8; ++v) {
+                        const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
+                        ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
+                    }
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r1[j]),
+                        red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r[j]),
                                            ix[j]);
                 }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_uempty + 8 * us);
             }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_uempty + 8 * us);
         }
         }
     }
