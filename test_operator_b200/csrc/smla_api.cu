@@ -199,14 +199,13 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     __nv_bfloat16* ds_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.ds_off);
     float* delta = reinterpret_cast<float*>(ws + pl.delta_off);
 
-    CUtensorMap tm_qnh, tm_donh, tm_qhp, tm_dohp, tm_kv, tm_s, tm_ds;
+    CUtensorMap tm_qnh, tm_donh, tm_qhp, tm_dohp, tm_s, tm_ds;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
     bool ok = true;
     ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
     ok &= make_map_2d(&tm_donh, p->dO, kDV, qrows, kDV * 2, 64, HP / 2);
     ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
     ok &= make_map_2d(&tm_dohp, p->dO, kDV, qrows, kDV * 2, 64, HP);
-    ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
     // S / dS scratch: the dkv kernel loads [128 keys x 64 heads] boxes, the dq kernel [64 keys x 64 heads]
     CUtensorMap tm_s128, tm_ds128;
     ok &= make_map_scratch(&tm_s128, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 128);
@@ -266,7 +265,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DQ) {
-            smla_dq_kernel<HP, kSplitChunk, kQChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_ds, kp);
+            smla_dq_kernel<HP, kSplitChunk, kQChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_ds, kp);
             ++g_last_launches;
         }
     }
@@ -327,11 +326,10 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     using namespace smla;
     float* logits = reinterpret_cast<float*>(ws + pl.logits_off);
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
-    CUtensorMap tm_qnh, tm_kv, tm_s;
+    CUtensorMap tm_qnh, tm_s;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
     bool ok = true;
     ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
-    ok &= make_map_2d(&tm_kv, p->kv, kDQK, uint64_t(p->s_kv), kDQK * 2, 64, 1);
     ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, true>, rp::Cfg<HP, true>::kSmemBytes);
@@ -365,7 +363,7 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
         if (pairs <= 0) return SMLA_ERR_LAUNCH;
         smla_recompute_pair_kernel<HP, true><<<2 * (nq < pairs ? nq : pairs), rp::kThreads, rp::Cfg<HP, true>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
         smla_fwd_softmax_kernel<HP><<<nq, 512, 0, st>>>(kp);
-        smla_dq_kernel<HP, kVChunks / 2, kVChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_kv, tm_s, kp);
+        smla_dq_kernel<HP, kVChunks / 2, kVChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_s, kp);
         g_last_launches += 3;
     }
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;

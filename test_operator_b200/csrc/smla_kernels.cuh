@@ -828,7 +828,6 @@ constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
 constexpr int kStages = 3;
-constexpr int kTmaChunks = 0;   // column chunks of a tile routed through TMA gather4 instead of cp.async (measured slower)
 template <int HP> struct Cfg {
     static constexpr int kKgBytes = 5 * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
@@ -842,7 +841,7 @@ template <int HP> struct Cfg {
 
 template <int HP, int kSplit, int kTotal>
 __global__ void __launch_bounds__(dq::kThreads, 1)
-smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
+smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
     using C = Cfg<HP>;
     const int part = blockIdx.x & 1;
@@ -891,55 +890,46 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant_
         const uint32_t dst0 = s_base + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + chunk0 * 128 + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
+        // the indices of a tile are loaded one tile ahead, so that their latency is never in front of the copies
+        int idx_next[2];
+        auto load_idx = [&](int tile) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int key = tile * kTileKeys + r0 + 32 * i;
+                idx_next[i] = (tile < n_tiles && key < p.topk) ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+            }
+        };
+        load_idx(0);
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int s = tile % kStages;
             const char* src[2];
             uint32_t nb[2];   // 0: slot out of range, read nothing and land zeros (no shared stand-in row: it would be a hot spot)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int key = tile * kTileKeys + r0 + 32 * i;
-                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                const bool in_range = idx >= 0 && idx < p.s_kv;
+                const bool in_range = idx_next[i] >= 0 && idx_next[i] < p.s_kv;
                 nb[i] = in_range ? 16u : 0u;
-                src[i] = kvb + static_cast<size_t>(in_range ? idx : 0) * (kDQK * 2);
+                src[i] = kvb + static_cast<size_t>(in_range ? idx_next[i] : 0) * (kDQK * 2);
             }
+            load_idx(tile + 1);
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);
             const uint32_t d = dst0 + s * C::kStage;
-            for (int c = kTmaChunks; c < n_ch; ++c) {
+            for (int c = 0; c < n_ch; ++c) {
                 cp_async16_zfill_hint(d + c * 8192, src[0] + c * 128, nb[0], pol_keep);
                 cp_async16_zfill_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, nb[1], pol_keep);
             }
             cp_async_mbar_arrive_noinc(bar_full + 8 * s);
         }
     } else if (warp == 13) {
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_ds);
-            tma_prefetch_desc(&tm_kv);
-        }
+        if (lane == 0) tma_prefetch_desc(&tm_ds);
         const uint64_t pol_stream = l2_policy_evict_first();
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            const int s = tile % kStages;
-            int r[4] = {0, 0, 0, 0};
-            if (lane < 16) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int key = tile * kTileKeys + lane * 4 + k;
-                    int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : 0;
-                    r[k] = min(max(idx, 0), p.s_kv - 1);
-                }
-            }
-            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4, kPollSleepNs);
-            const uint32_t dst = s_base + s * C::kStage;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes + kTmaChunks * 8192);
+        if (lane == 0) {
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const int s = tile % kStages;
+                mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4, kPollSleepNs);
+                const uint32_t dst = s_base + s * C::kStage;
+                mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes);
                 // box = 64 keys of every head block -> [HP/8][64 keys][8 heads]
                 tma_load_4d_hint(dst + C::kKgBytes, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_full + 8 * s, pol_stream);
-            }
-            __syncwarp();
-            if (lane < 16) {
-                for (int c = 0; c < kTmaChunks; ++c)
-                    tma_gather4(dst + c * 8192 + lane * 512, &tm_kv, 64 * (chunk0 + c), r[0], r[1], r[2], r[3],
-                                bar_full + 8 * s);
             }
         }
     } else if (warp == 12) {
