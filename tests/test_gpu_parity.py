@@ -68,6 +68,9 @@ CASES_SMALL = [
     ("h8_one_query", 1, 40, 8, 40, "uniform", 0.3),
     ("h128_all_slots_invalid_some_rows", 6, 128, 128, 64, "uniform", 0.0),
     ("h128_skewed", 4, 2048, 128, 128, "skewed", 0.1),
+    # more queries than the persistent recompute clusters / dkv CTAs of a B200: every CTA walks over several queries
+    ("h128_many_queries", 401, 1024, 128, 256, "uniform", 0.1),
+    ("h64_many_queries_two_tiles", 333, 700, 64, 300, "uniform", 0.05),
 ]
 
 
