@@ -229,6 +229,75 @@ def mla_bwd(
     return dQ, dKV
 
 
+def _apply_topk_length(indices: torch.Tensor, topk_length: Optional[torch.Tensor]) -> torch.Tensor:
+    """Slots at or beyond a query's `topk_length` become unused (-1)."""
+    if topk_length is None:
+        return indices
+    _check(topk_length.shape == indices.shape[:-1] and not topk_length.is_floating_point(),
+           "topk_length must be an integer tensor shaped like indices without its last dimension")
+    slot = torch.arange(indices.shape[-1], device=indices.device)
+    return torch.where(slot < topk_length.unsqueeze(-1).to(indices.device), indices, indices.new_full((), -1)).contiguous()
+
+
+def mla_bwd_batched(q, kv, dO, lse, O, indices, topk_length: Optional[torch.Tensor] = None, **kwargs):
+    """Backward for a batch of independent sequences of equal shape, so that callers stop looping themselves.
+
+    q / dO / O [B, s_q, h_q, d], kv [B, s_kv, 576] (or [B, s_kv, 1, 576]), lse [B, s_q, h_q], indices [B, s_q, topk]
+    with values relative to the own sequence's kv; `topk_length` [B, s_q] (optional) limits the slots in use per query,
+    the per-query field of the reference's richer parameter block (`dq_test/dq_phase_capture.cuh:107-109`).  One
+    workspace serves all sequences; the kernels of consecutive sequences queue on the current stream.  Returns
+    (dQ [B, s_q, h_q, 576] bf16, dKV fp32 shaped like kv).  Keyword arguments as for `mla_bwd` (without out_dkv).
+    """
+    _check(q.dim() == 4 and kv.dim() in (3, 4) and indices.dim() == 3, "batched tensors need a leading batch dimension")
+    B = q.shape[0]
+    _check(all(t.shape[0] == B for t in (kv, dO, lse, O, indices)), "batch sizes differ")
+    _check("out_dkv" not in kwargs and "accumulate" not in kwargs, "mla_bwd_batched allocates its outputs")
+    idx = _apply_topk_length(indices, topk_length)
+    ws = kwargs.pop("workspace", None) or workspace_for(q[0], kv[0], idx[0], kwargs.pop("workspace_budget", 0))
+    dQ = torch.empty_like(q)
+    dKV = torch.empty(kv.shape, dtype=torch.float32, device=q.device)
+    for b in range(B):
+        dq_b, _ = mla_bwd(q[b], kv[b], dO[b], lse[b], O[b], idx[b], out_dkv=dKV[b], workspace=ws, **kwargs)
+        dQ[b].copy_(dq_b)
+    return dQ, dKV
+
+
+def mla_bwd_varlen(q, kv, dO, lse, O, indices, cu_seqlens_q, cu_seqlens_kv, topk_length: Optional[torch.Tensor] = None,
+                   **kwargs):
+    """Backward for sequences of different lengths packed along the first dimension.
+
+    q / dO / O [T_q, h_q, d], lse [T_q, h_q], indices [T_q, topk], kv [T_kv, 576]; sequence i owns query rows
+    cu_seqlens_q[i]:cu_seqlens_q[i+1] and kv rows cu_seqlens_kv[i]:cu_seqlens_kv[i+1] (host integer sequences or CPU
+    tensors, as in the usual varlen attention interfaces).  Index values are relative to the own sequence's first kv
+    row; `q_start_index_s` applies to every sequence from its own first query.  Returns (dQ [T_q, h_q, 576] bf16,
+    dKV [T_kv, 576] fp32).  Empty sequences are allowed.
+    """
+    cq = [int(v) for v in cu_seqlens_q]
+    ck = [int(v) for v in cu_seqlens_kv]
+    _check(len(cq) == len(ck) and len(cq) >= 2 and cq[0] == 0 and ck[0] == 0, "cu_seqlens must start at 0 and match in length")
+    _check(cq[-1] == q.shape[0] and ck[-1] == kv.shape[0], "cu_seqlens do not cover q / kv")
+    _check(all(a <= b for a, b in zip(cq, cq[1:])) and all(a <= b for a, b in zip(ck, ck[1:])), "cu_seqlens must not decrease")
+    _check("out_dkv" not in kwargs and "accumulate" not in kwargs, "mla_bwd_varlen allocates its outputs")
+    idx = _apply_topk_length(indices, topk_length)
+    budget = kwargs.pop("workspace_budget", 0)
+    ws = kwargs.pop("workspace", None)
+    dQ = torch.empty_like(q)
+    dKV = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)      # sequences without queries keep zeros
+    longest = max(range(len(cq) - 1), key=lambda i: cq[i + 1] - cq[i])
+    for i in range(len(cq) - 1):
+        q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i + 1]
+        if q1 == q0 or k1 == k0:
+            _check(q1 == q0, "a sequence with queries needs kv rows")
+            continue
+        if ws is None:       # sized for the longest sequence; shorter ones take fewer passes through it
+            l0, l1 = cq[longest], cq[longest + 1]
+            ws = workspace_for(q[l0:l1], kv[k0:k1], idx[l0:l1], budget)
+        dq_i, _ = mla_bwd(q[q0:q1], kv[k0:k1], dO[q0:q1], lse[q0:q1], O[q0:q1], idx[q0:q1], out_dkv=dKV[k0:k1],
+                          workspace=ws, **kwargs)
+        dQ[q0:q1].copy_(dq_i)
+    return dQ, dKV
+
+
 def mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: Optional[float] = None,
             q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True, workspace: Optional[Workspace] = None,
             workspace_budget: int = 0, check_device_status: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
