@@ -164,34 +164,6 @@ int resident_pairs(K kernel, int threads, int smem_bytes) {
     return n;
 }
 
-int sm_count() {
-    static std::mutex mu;
-    static int cached[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    std::lock_guard<std::mutex> lock(mu);
-    if (cached[dev] > 0) return cached[dev];
-    int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) return 0;
-    cached[dev] = sms;
-    return sms;
-}
-
-// Grid of a persistent kernel whose CTAs each stay with one d-part: `grid` CTAs in all, the first `split0` on
-// d-part 0.  The parts cost about cost0 : cost1, and the CTAs are shared out in that ratio.
-void split_grid(int nq, int cost0, int cost1, int* grid, int* split0) {
-    const int sms = sm_count();
-    int g = sms < 2 ? 2 : sms;
-    if (g > 2 * nq) g = 2 * nq;
-    int s0 = (g * cost0 + (cost0 + cost1) / 2) / (cost0 + cost1);
-    if (s0 < 1) s0 = 1;
-    if (s0 > g - 1) s0 = g - 1;
-    if (s0 > nq) s0 = nq;            // never more CTAs on a part than there are queries
-    if (g - s0 > nq) g = s0 + nq;
-    *grid = g;
-    *split0 = s0;
-}
-
 template <int HP>
 int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages) {
     using namespace smla;
@@ -207,16 +179,13 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
     ok &= make_map_2d(&tm_dohp, p->dO, kDV, qrows, kDV * 2, 64, HP);
     // S / dS scratch: the dkv kernel loads [128 keys x 64 heads] boxes, the dq kernel [64 keys x 64 heads]
-    CUtensorMap tm_s128, tm_ds128;
-    ok &= make_map_scratch(&tm_s128, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 128);
-    ok &= make_map_scratch(&tm_ds128, ds_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 128);
     ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     ok &= make_map_scratch(&tm_ds, ds_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
 
     // per device, so set on every call (cheap) rather than once per process
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, false>, rp::Cfg<HP, false>::kSmemBytes);
-    attr_ok &= set_smem(smla_dkv_kernel<HP>, dk::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_dkv_pair_kernel<HP>, dp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dq_kernel<HP, kSplitChunk, kQChunks>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
@@ -259,9 +228,9 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DKV) {
-            int grid = 0;
-            split_grid(nq, 320, 256, &grid, &kp.split0);     // reductions into 320 and 256 columns of dKV
-            smla_dkv_kernel<HP><<<grid, dk::kThreads, dk::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s128, tm_ds128, kp);
+            const int pairs = resident_pairs(smla_dkv_pair_kernel<HP>, dp::kThreads, dp::Cfg<HP>::kSmemBytes);
+            if (pairs <= 0) return SMLA_ERR_LAUNCH;
+            smla_dkv_pair_kernel<HP><<<2 * (nq < pairs ? nq : pairs), dp::kThreads, dp::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
             ++g_last_launches;
         }
         if (stages & SMLA_STAGE_DQ) {

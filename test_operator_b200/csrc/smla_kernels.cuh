@@ -48,7 +48,6 @@ struct KParams {
     int* g_err;
     int q0;                   // first query (global row) of this pass
     int nq;                   // queries in this pass
-    int split0;               // dkv / dq kernels: CTAs [0, split0) take d-part 0, the others d-part 1
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
@@ -548,202 +547,210 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
 }
 
 // =============================================================================================
-// dkv: persistent CTAs, each working through (query, d-part) items of one d-part.  d-part 0 owns columns [0,320),
-// part 1 owns [320,576).
-//   resident   Q^T and dO^T of the part: chunks [HP heads x 64 d] read MN-major as the A operand
-//              (M = d, 128 rows = two adjacent chunks, K = heads)
-//   warp 0     producer: resident chunks once, then per 128-key tile the S and dS scratch tiles
-//              [128 keys x HP heads] (B operand, K-major); one shared-memory stage
-//   warp 1     UMMA issuer: unit = (tile, block of 128 d rows): acc[128 d, 128 keys] = dO^T . S + Q^T . dS
-//              into a ring of four 128-column TMEM units, so the MMAs run ahead of the drain
-//   warps 2-17 drain, two groups of eight taking alternate units: thread = d row, each warp owns 32 d rows x 64 keys
-//              of a unit; one fp32 reduction per key, 32 lanes -> 128 contiguous bytes of dKV
-// Part 0's third block has 64 real rows (d 256..319); its other 64 rows read a neighbouring chunk
-// and are never drained.  Part 1 pads dO with a zero chunk (d 512..575 has no V).
+// dkv as persistent 2-CTA clusters: one pair per query, all 576 columns of d.
+//
+//   dKV^T[d, key] = dO^T . S + Q^T . dS with cta_group::2 UMMAs of M = 256 rows of d (128 per CTA) x N = 128 keys
+//   (64 supplied by each CTA): a CTA reads 4 KB of A and 2 KB of B per 64 cycles of math, where the single-CTA
+//   128x128x16 form reads 8 KB, which is all the shared-memory bandwidth there is.  The S / dS scratch of a query is
+//   read once (half a tile per CTA) instead of once per d-part.
+//
+//   blocks of d   0: [0,256)   1: [256,512)   2: [512,576) (Q^T . dS only: V has 512 columns)
+//   CTA r holds rows [128 r, 128 r + 128) of blocks 0 and 1 as resident Q^T / dO^T chunk pairs.  Block 2 is issued
+//   from the slot pair (3, 4) in both CTAs: slot 4 holds chunk 8 in both, so both compute the same 64 real rows in
+//   lanes 64-127 (lanes 0-63 repeat chunk 3's rows and are dropped); CTA (tile & 1) drains them, which keeps the
+//   reductions of the two CTAs equal over two tiles.
+//   warp 0      producer: resident chunks per query; per 128-key tile this CTA's 64 keys of S and dS, two stages
+//   warp 1      even CTA: UMMA issuer for the pair; odd CTA: relays "my half landed" to the even CTA's barriers
+//   warps 2-17  drain, two groups of eight on alternate accumulator units (ring of four 128-column units per CTA):
+//               lane = d row, one predicated fp32 reduction per key = 128 contiguous bytes of dKV
 // =============================================================================================
-namespace dk {
-constexpr int kThreads = 576;   // warp 0 producer, warp 1 UMMA issuer, warps 2-17 drain (two groups of eight)
+namespace dp {
+constexpr int kThreads = 576;
 constexpr int kTileKeys = 128;
-constexpr int kResChunks = 5;
-constexpr int kUnits = 4;       // TMEM accumulator ring: 4 x 128 columns
+constexpr int kUnits = 4;
+constexpr int kTileStages = 2;
 template <int HP> struct Cfg {
-    static constexpr int kChunk = HP * 128;                 // resident chunk bytes
-    static constexpr int kTileMat = (HP / 64) * 16384;      // one S (or dS) tile: [128 keys x HP heads]
-    static constexpr int kStage = 2 * kTileMat;
-    static constexpr int kOffQ = 0;
-    static constexpr int kOffDO = kResChunks * kChunk;
-    static constexpr int kOffStage = 2 * kResChunks * kChunk;
-    static constexpr int kOffMisc = kOffStage + kStage;
-    static constexpr int kOffIdx = kOffMisc + 128;          // [2 groups][2 tile parities][2 key halves][64] int
-    static constexpr int kSmemBytes = kOffMisc + 128 + 2048 + 896;   // all of the 227 KB; 896 B alignment slack
+    static constexpr int kChunk = HP * 128;                 // resident chunk [HP heads x 64 d] bytes
+    static constexpr int kHalfMat = HP * 128;               // S (or dS) of 64 keys: [HP/8][64 keys][8 heads]
+    static constexpr int kStage = 2 * kHalfMat;             // S then dS
+    static constexpr int kOffQ = 0;                         // 5 slots
+    static constexpr int kOffDO = 5 * kChunk;               // 4 slots
+    static constexpr int kOffStage = 9 * kChunk;
+    static constexpr int kOffMisc = kOffStage + kTileStages * kStage;
+    static constexpr int kOffIdx = kOffMisc + 256;          // [2 groups][2 tile parities][2 key halves][64] int
+    static constexpr int kSmemBytes = kOffMisc + 256 + 2048 + 1024;
 };
-}  // namespace dk
+}  // namespace dp
 
 template <int HP>
-__global__ void __launch_bounds__(dk::kThreads, 1)
-smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
-    using namespace dk;
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dp::kThreads, 1)
+smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
+    using namespace dp;
     using C = Cfg<HP>;
-    // Persistent: CTAs [0, split0) work on d-part 0 of queries b, b + split0, ...; the rest on d-part 1.  The split
-    // follows the parts' cost (320 : 256 columns of reductions) so that both groups finish together.
-    const int part = static_cast<int>(blockIdx.x) >= p.split0;
-    const int q_first = part ? blockIdx.x - p.split0 : blockIdx.x;
-    const int q_stride = part ? gridDim.x - p.split0 : p.split0;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1;
+    const int n_pairs = gridDim.x >> 1;
     const int nq = p.nq;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n_blk = part ? 2 : 3;
-    const int chunk0 = part ? kSplitChunk : 0;
-    const int n_q = part ? kQChunks - kSplitChunk : kSplitChunk;           // 4 : 5
-    const int n_do = part ? kVChunks - kSplitChunk : kSplitChunk;          // 3 : 5 (real dO chunks)
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t s_base = smem_u32(smem);
-    if (smem - smem_raw > 896) {   // the carve-up below would run past the allocation (uniform across the CTA)
-        if (threadIdx.x == 0) atomicCAS(p.g_err, 0, kErrDkv + 9);
-        return;
-    }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffMisc);
-    const uint32_t bar_sfull = smem_u32(bars);          // 1  S tile landed
-    const uint32_t bar_sempty = bar_sfull + 8;          // 1  the tile's UMMAs on S finished
-    const uint32_t bar_dsfull = bar_sempty + 8;         // 1  dS tile landed
-    const uint32_t bar_dsempty = bar_dsfull + 8;        // 1  the tile's UMMAs on dS finished
-    const uint32_t bar_res = bar_dsempty + 8;           // 1  resident Q^T / dO^T of the current query landed
-    const uint32_t bar_resfree = bar_res + 8;           // 1  all UMMAs of the current query finished
-    const uint32_t bar_ufull = bar_resfree + 8;         // [kUnits]
-    const uint32_t bar_uempty = bar_ufull + 8 * kUnits; // [kUnits]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (6 + 2 * kUnits));
-    static_assert(8 * (6 + 2 * kUnits) + 8 <= 128, "barrier area");
+    const uint32_t bar_tfull = smem_u32(bars);                        // [2] tile stage landed (even CTA: in both CTAs)
+    const uint32_t bar_tempty = bar_tfull + 8 * kTileStages;          // [2] the tile's UMMAs finished
+    const uint32_t bar_res = bar_tempty + 8 * kTileStages;            // 1  resident chunks landed (even CTA: in both CTAs)
+    const uint32_t bar_resfree = bar_res + 8;                         // 1  all UMMAs of the query finished
+    const uint32_t bar_ufull = bar_resfree + 8;                       // [kUnits] accumulator unit complete
+    const uint32_t bar_uempty = bar_ufull + 8 * kUnits;               // [kUnits] (even CTA) both CTAs have drained the unit
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (2 * kTileStages + 2 + 2 * kUnits));
+    static_assert(8 * (2 * kTileStages + 2 + 2 * kUnits) + 8 <= 256, "barrier area");
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const WaitCtx wc{p.g_err, s_abort};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
-        mbar_init(bar_sfull, 1);
-        mbar_init(bar_sempty, 1);
-        mbar_init(bar_dsfull, 1);
-        mbar_init(bar_dsempty, 1);
-        mbar_init(bar_res, 1);
+        for (int i = 0; i < kTileStages; ++i) {
+            mbar_init(bar_tfull + 8 * i, rank == 0 ? 2 : 1);   // own expect_tx arrival (+ the odd CTA's relayed one)
+            mbar_init(bar_tempty + 8 * i, 1);
+        }
+        mbar_init(bar_res, rank == 0 ? 2 : 1);
         mbar_init(bar_resfree, 1);
         for (int i = 0; i < kUnits; ++i) {
             mbar_init(bar_ufull + 8 * i, 1);
-            mbar_init(bar_uempty + 8 * i, 8);
+            mbar_init(bar_uempty + 8 * i, 16);                 // eight drain warps of the unit's group in each CTA
         }
         fence_mbar_init();
     }
-    if (part == 1) {  // zero chunk standing in for dO columns 512..575
-        uint4* z = reinterpret_cast<uint4*>(smem + C::kOffDO + n_do * C::kChunk);
-        for (int i = threadIdx.x; i < C::kChunk / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
-        fence_proxy_async_smem();
-    }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
+        tmem_alloc_2cta(smem_u32(tmem_slot), 512);
+        tmem_relinquish_2cta();
     }
     tc_fence_before_sync();
     __syncthreads();
+    cluster_sync_all();          // barriers of both CTAs are initialised before anyone signals across
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const int n_tiles = p.topk_pad / kTileKeys;
 
     if (warp == 0) {
+        // ------------------------------------------------------------------ producer
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_do);
             tma_prefetch_desc(&tm_s);
             tma_prefetch_desc(&tm_ds);
             const uint64_t pol_stream = l2_policy_evict_first();
-            uint32_t gtile = 0, k = 0;
-            for (int ql = q_first; ql < nq; ql += q_stride, ++k) {
+            int s = 0;
+            uint32_t ph = 1, k = 0;        // ph: parity that means "stage free" in the current pass over the ring
+            for (int ql = pair; ql < nq; ql += n_pairs, ++k) {
                 // the resident operands are replaced once the previous query's UMMAs are done; the drain warps
                 // meanwhile still work through the accumulator ring, so the reductions do not pause
                 if (k) mbar_wait(bar_resfree, (k - 1) & 1, wc, kErrDkv + 6, kPollSleepNs);
-                mbar_arrive_expect_tx(bar_res, (n_q + n_do) * C::kChunk);
+                mbar_arrive_expect_tx(bar_res, 9 * C::kChunk);
                 const int row0 = (p.q0 + ql) * p.h_q;
-                for (int j = 0; j < n_q; ++j)
-                    tma_load_2d_hint(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * (chunk0 + j), row0, bar_res, pol_stream);
-                for (int j = 0; j < n_do; ++j)
-                    tma_load_2d_hint(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * (chunk0 + j), row0, bar_res, pol_stream);
-                for (int tile = 0; tile < n_tiles; ++tile, ++gtile) {
-                    // box = 128 keys of every head block -> [HP/8][128 keys][8 heads].  S and dS have a buffer and a
-                    // pair of barriers each: the next tile's S comes in while this tile's dS is being multiplied,
-                    // and the other way round.
-                    const uint32_t dst = s_base + C::kOffStage;
-                    mbar_wait(bar_sempty, (gtile & 1) ^ 1, wc, kErrDkv + 1, kPollSleepNs);
-                    mbar_arrive_expect_tx(bar_sfull, C::kTileMat);
-                    tma_load_4d_hint(dst, &tm_s, 0, tile * (kTileKeys / 32), 0, ql, bar_sfull, pol_stream);
-                    mbar_wait(bar_dsempty, (gtile & 1) ^ 1, wc, kErrDkv + 7, kPollSleepNs);
-                    mbar_arrive_expect_tx(bar_dsfull, C::kTileMat);
-                    tma_load_4d_hint(dst + C::kTileMat, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_dsfull, pol_stream);
+                for (int j = 0; j < 4; ++j) {          // slots 0..3: chunks {2r, 2r+1} of block 0 and block 1
+                    const int chunk = (j >> 1) * 4 + 2 * static_cast<int>(rank) + (j & 1);
+                    tma_load_2d_hint(s_base + C::kOffQ + j * C::kChunk, &tm_q, 64 * chunk, row0, bar_res, pol_stream);
+                    tma_load_2d_hint(s_base + C::kOffDO + j * C::kChunk, &tm_do, 64 * chunk, row0, bar_res, pol_stream);
+                }
+                tma_load_2d_hint(s_base + C::kOffQ + 4 * C::kChunk, &tm_q, 64 * 8, row0, bar_res, pol_stream);
+                for (int tile = 0; tile < n_tiles; ++tile) {
+                    mbar_wait(bar_tempty + 8 * s, ph, wc, kErrDkv + 1, kPollSleepNs);
+                    mbar_arrive_expect_tx(bar_tfull + 8 * s, C::kStage);
+                    const uint32_t dst = s_base + C::kOffStage + s * C::kStage;
+                    // box = this CTA's 64 keys of every head block -> [HP/8][64 keys][8 heads]
+                    const int kb = tile * (kTileKeys / 32) + 2 * static_cast<int>(rank);
+                    tma_load_4d_hint(dst, &tm_s, 0, kb, 0, ql, bar_tfull + 8 * s, pol_stream);
+                    tma_load_4d_hint(dst + C::kHalfMat, &tm_ds, 0, kb, 0, ql, bar_tfull + 8 * s, pol_stream);
+                    if (++s == kTileStages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(128, 128, 1, 0);  // A MN-major (d contiguous), B K-major
-            const uint32_t st_s = s_base + C::kOffStage;
-            const uint32_t st_ds = st_s + C::kTileMat;
-            int unit = 0;
-            uint32_t gtile = 0, k = 0;
-            for (int ql = q_first; ql < nq; ql += q_stride, ++k) {
-            mbar_wait(bar_res, k & 1, wc, kErrDkv + 2);
-            for (int tile = 0; tile < n_tiles; ++tile, ++gtile) {
-                // pass 1: dO^T . S into the tile's accumulators (a free ring unit each); pass 2: += Q^T . dS
-                mbar_wait(bar_sfull, gtile & 1, wc, kErrDkv + 4);
-                for (int blk = 0; blk < n_blk; ++blk) {
-                    const int u = unit + blk, us = u % kUnits;
-                    mbar_wait(bar_uempty + 8 * us, ((u / kUnits) & 1) ^ 1, wc, kErrDkv + 3);
-                    tc_fence_after_sync();
-                    const uint32_t d = tmem + us * 128;
-                    // Part 0's third block has one real chunk (d 256..319).  On odd tiles it is placed in the upper
-                    // 64 rows of the block (the lower 64 repeat chunk 3 and are dropped), on even tiles in the lower
-                    // 64: the drain of that block then alternates between the two halves of the drain warps, i.e.
-                    // between the SM sub-partitions, whose reduction issue rate is what bounds this kernel.
-                    const int shift = (part == 0 && blk == 2 && (tile & 1)) ? C::kChunk : 0;
-                    const uint32_t a_do = s_base + C::kOffDO + 2 * blk * C::kChunk - shift;
-#pragma unroll
-                    for (int ks = 0; ks < HP / 16; ++ks)
-                        umma_ss(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
-                                make_smem_desc(st_s + ks * 4096, 2048, 128, kSwizzleNone), idesc, ks != 0);
+            if (rank == 1) {
+                // -------------------------------------------------------------- relay "landed" to the even CTA
+                // TMA wrote the data (async proxy) and the tensor core reads it (async proxy): no proxy fence; the
+                // relaxed arrive costs a few cycles where a cluster-scope release costs hundreds.
+                int s = 0;
+                uint32_t ph = 0, k = 0;
+                for (int ql = pair; ql < nq; ql += n_pairs, ++k) {
+                    mbar_wait(bar_res, k & 1, wc, kErrDkv + 10);
+                    mbar_arrive_cluster_relaxed(map_to_cta(bar_res, 0));
+                    for (int tile = 0; tile < n_tiles; ++tile) {
+                        mbar_spin(bar_tfull + 8 * s, ph, wc, kErrDkv + 11);
+                        mbar_arrive_cluster_relaxed(map_to_cta(bar_tfull + 8 * s, 0));
+                        if (++s == kTileStages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
                 }
-                umma_commit(bar_sempty);
-                mbar_wait(bar_dsfull, gtile & 1, wc, kErrDkv + 8);
-                for (int blk = 0; blk < n_blk; ++blk) {
-                    const int us = (unit + blk) % kUnits;
-                    const uint32_t d = tmem + us * 128;
-                    const int shift = (part == 0 && blk == 2 && (tile & 1)) ? C::kChunk : 0;
-                    const uint32_t a_q = s_base + C::kOffQ + 2 * blk * C::kChunk - shift;
+            } else {
+                // -------------------------------------------------------------- UMMA issuer for the pair
+                constexpr uint32_t idesc = make_idesc_bf16(256, 128, 1, 0);   // A MN-major (d contiguous), B K-major
+                int s = 0;
+                uint32_t ph = 0, k = 0, unit = 0;
+                for (int ql = pair; ql < nq; ql += n_pairs, ++k) {
+                    mbar_wait(bar_res, k & 1, wc, kErrDkv + 2);
+                    for (int tile = 0; tile < n_tiles; ++tile) {
+                        mbar_wait(bar_tfull + 8 * s, ph, wc, kErrDkv + 4);
+                        const uint32_t st_s = s_base + C::kOffStage + s * C::kStage;
+                        const uint32_t st_ds = st_s + C::kHalfMat;
+                        for (int blk = 0; blk < 3; ++blk, ++unit) {
+                            const int us = unit % kUnits;
+                            mbar_wait(bar_uempty + 8 * us, ((unit / kUnits) & 1) ^ 1, wc, kErrDkv + 3);
+                            tc_fence_after_sync();
+                            const uint32_t d = tmem + us * 128;
+                            // each CTA's 128 rows: slot pair (0,1), (2,3) or, for block 2, (3,4)
+                            const int slot = blk == 2 ? 3 : 2 * blk;
+                            if (blk < 2) {
+                                const uint32_t a_do = s_base + C::kOffDO + slot * C::kChunk;
 #pragma unroll
-                    for (int ks = 0; ks < HP / 16; ++ks)
-                        umma_ss(d, make_smem_desc(a_q + ks * 2048, C::kChunk, 1024, kSwizzle128),
-                                make_smem_desc(st_ds + ks * 4096, 2048, 128, kSwizzleNone), idesc, 1);
-                    umma_commit(bar_ufull + 8 * us);
+                                for (int ks = 0; ks < HP / 16; ++ks)
+                                    umma_ss_2cta(d, make_smem_desc(a_do + ks * 2048, C::kChunk, 1024, kSwizzle128),
+                                                 make_smem_desc(st_s + ks * 2048, 1024, 128, kSwizzleNone), idesc, ks != 0);
+                            }
+                            const uint32_t a_q = s_base + C::kOffQ + slot * C::kChunk;
+#pragma unroll
+                            for (int ks = 0; ks < HP / 16; ++ks)
+                                umma_ss_2cta(d, make_smem_desc(a_q + ks * 2048, C::kChunk, 1024, kSwizzle128),
+                                             make_smem_desc(st_ds + ks * 2048, 1024, 128, kSwizzleNone), idesc,
+                                             blk < 2 || ks != 0);
+                            umma_commit_2cta_mask(bar_ufull + 8 * us, 3);
+                        }
+                        umma_commit_2cta_mask(bar_tempty + 8 * s, 3);
+                        if (++s == kTileStages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+                    umma_commit_2cta_mask(bar_resfree, 3);
                 }
-                umma_commit(bar_dsempty);
-                unit += n_blk;
-            }
-            umma_commit(bar_resfree);
             }
         }
     } else {
-        // Two groups of eight drain warps take alternate accumulator units.  A unit costs a warp a fixed part (wait for
-        // the UMMAs, accumulator load, indices: ~1.4k cycles) and the issue of 64 reductions (~1.8k cycles at the SM's
-        // reduction rate); with one group the two add up, with two groups one group's fixed part runs under the other
-        // group's reductions.
+        // ------------------------------------------------------------------ drain (this CTA's 128 rows of every unit)
+        // Two groups of eight warps take alternate units: one group's fixed cost per unit (wait, accumulator load,
+        // indices) runs under the other group's reductions.
         const int dw = warp - 2;                // 0..15
         const int grp = dw >> 3;
         const int quarter = warp & 3;           // the TMEM lane quarter a warp may read is warp % 4
         const int e = (dw >> 2) & 1;            // which 64 keys of the 128-key tile this warp scatters
         const int member = dw & 3;              // the four warps of a (group, key half) share one index buffer
-        const int d_part0 = chunk0 * 64;
-        const int upq = n_tiles * n_blk;        // units per query: even, because top-k is padded to 256 keys
+        const int upq = n_tiles * 3;            // units per query: even, because top-k is padded to 256 keys
         // index buffers [group][tile parity][key half][64]: filled by member 0 from registers it loaded one tile ahead,
         // published with a named barrier of the four warps.  Every tile shows up in both groups' unit sequences and
         // the barrier keeps the four within one tile of each other, so two buffers per (group, key half) suffice.
         int* idx_base = reinterpret_cast<int*>(smem + C::kOffIdx) + (grp * 4 + e) * 64;
         const int bar_id = 1 + grp * 2 + e;
+        const uint32_t uempty0 = map_to_cta(bar_uempty, 0);
         int pf[2] = {-1, -1};
         auto fetch_idx = [&](int ql, int tile) {
 #pragma unroll
@@ -754,60 +761,66 @@ smla_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 pf[i] = (ql < nq && slot_valid(idx, qg, p)) ? idx : -1;
             }
         };
-        if (member == 0) fetch_idx(q_first, 0);
+        if (member == 0) fetch_idx(pair, 0);
         uint32_t qn = 0;
-        for (int ql = q_first; ql < nq; ql += q_stride, ++qn) {
-        int last_tile = -1;
-        for (int ul = grp; ul < upq; ul += 2) {
-            const int tile = ul / n_blk, blk = ul - tile * n_blk;
-            const uint32_t unit = qn * upq + ul;
-            const int us = unit % kUnits;
-            int* idx_s = idx_base + (tile & 1) * 128;
-            if (tile != last_tile) {
-                last_tile = tile;
-                if (member == 0) {
-                    idx_s[lane] = pf[0];
-                    idx_s[32 + lane] = pf[1];
-                }
-                asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-                if (member == 0) {
-                    if (tile + 1 < n_tiles) fetch_idx(ql, tile + 1);
-                    else fetch_idx(ql + q_stride, 0);
-                }
-            }
-            mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
-            tc_fence_after_sync();
-            const bool upper = part == 0 && blk == 2 && (tile & 1);   // where the half block's real rows are
-            if (!(part == 0 && blk == 2 && (quarter >= 2) != upper)) {   // the other rows are never drained
-                float* out = p.dKV + d_part0 + blk * 128 + quarter * 32 + lane - (upper ? 64 : 0);
-                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + 32 * i, r);
-                    int ix[32];
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
-                        ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
+        for (int ql = pair; ql < nq; ql += n_pairs, ++qn) {
+            int last_tile = -1;
+            for (int ul = grp; ul < upq; ul += 2) {
+                const int tile = ul / 3, blk = ul - tile * 3;
+                const uint32_t unit = qn * upq + ul;
+                const int us = unit % kUnits;
+                int* idx_s = idx_base + (tile & 1) * 128;
+                if (tile != last_tile) {
+                    last_tile = tile;
+                    if (member == 0) {
+                        idx_s[lane] = pf[0];
+                        idx_s[32 + lane] = pf[1];
                     }
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK, __uint_as_float(r[j]),
-                                           ix[j]);
+                    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                    if (member == 0) {
+                        if (tile + 1 < n_tiles) fetch_idx(ql, tile + 1);
+                        else fetch_idx(ql + n_pairs, 0);
+                    }
                 }
+                mbar_wait(bar_ufull + 8 * us, (unit / kUnits) & 1, wc, kErrDkv + 5, kPollSleepNs);
+                tc_fence_after_sync();
+                // blocks 0, 1: every row is real (d = 256 blk + 128 rank + row).  Block 2: rows 64..127 are d 512..575
+                // in both CTAs; the CTA whose turn it is drains them.
+                const bool mine = blk < 2 || (quarter >= 2 && static_cast<uint32_t>(tile & 1) == rank);
+                if (mine) {
+                    const int d0 = blk < 2 ? 256 * blk + 128 * static_cast<int>(rank) : 512 - 64;
+                    float* out = p.dKV + d0 + quarter * 32 + lane;
+                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(taddr + 32 * i, r);
+                        int ix[32];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const int4 t = reinterpret_cast<const int4*>(idx_s)[8 * i + v];
+                            ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
+                        }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK,
+                                               __uint_as_float(r[j]), ix[j]);
+                    }
+                }
+                // the accumulator reads have completed (tcgen05.wait::ld), which is all the issuer needs to know
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(uempty0 + 8 * us);
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_uempty + 8 * us);
-        }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 512);
+    cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
+    if (warp == 1) tmem_dealloc_2cta(tmem, 512);
 }
+
 
 // =============================================================================================
 // dq: one CTA per (query, d-part); same d split as dkv; 14 warps.
