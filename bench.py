@@ -36,7 +36,7 @@ STAGE_NAMES = {2: "delta", 4: "recompute", 8: "dkv", 16: "dq"}
 # DRAM bytes (read + write) per query of each kernel at h_q 128 / top-k 2048, from the ncu captures summarised in
 # profiles/ (296-query case, dram__bytes_read.sum + dram__bytes_write.sum divided by 296; every kernel's DRAM
 # traffic grows in proportion to the number of queries).  None: no capture for that shape.
-DRAM_BYTES_PER_QUERY_H128_TOPK2048 = {"recompute": 1.349e6, "dkv": 2.859e6, "dq": 0.695e6}
+DRAM_BYTES_PER_QUERY_H128_TOPK2048 = {"recompute": 1.360e6, "dkv": 2.228e6, "dq": 0.703e6}
 # share of the 5504 FLOPs per slot each kernel carries: recompute = P + dP, dkv = dV + dK, dq = dQ
 STAGE_FLOP_SHARE = {4: (2 * 576 + 2 * 512) / 5504.0, 8: (2 * 512 + 2 * 576) / 5504.0, 16: 2 * 576 / 5504.0}
 
@@ -302,7 +302,7 @@ def run_ours(args):
     if mm:
         dom = max(mm, key=lambda k: mm[k]["ms"])
         peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))  # burst: kernel timed alone
-        roofline = {"bound": "tensor", "kernel": f"smla_{dom}_kernel", "achieved": mm[dom]["tflops"], "peak": peak,
+        roofline = {"bound": "tensor", "kernel": {"recompute": "smla_recompute_pair_kernel", "dkv": "smla_dkv_pair_kernel", "dq": "smla_dq_kernel"}[dom], "achieved": mm[dom]["tflops"], "peak": peak,
                     "unit": "TFLOP/s", "frac": mm[dom]["tflops"] / peak, "peak_kind": peak_kind + " burst",
                     "traffic": None}
         per_q = DRAM_BYTES_PER_QUERY_H128_TOPK2048.get(dom)
