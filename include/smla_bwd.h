@@ -130,6 +130,17 @@ typedef struct smla_bwd_workspace_layout {
 } smla_bwd_workspace_layout;
 int smla_bwd_get_workspace_layout(const smla_bwd_params* p, size_t workspace_bytes, smla_bwd_workspace_layout* out);
 
+/* Index inverse of the sparse pattern (a reusable pre-pass; the reference has no such operator, its validity rule
+ * is the one of mla_bwd/mla_bwd.cu:765-789): CSR by kv row of the valid slots.
+ *   row_ptr [s_kv + 1] i32: entries[row_ptr[r] .. row_ptr[r+1]) are the slots that chose kv row r;
+ *   entries [s_q * topk] i32: flat slot ids q * topk + slot, ascending inside a row (a fixed order: the result is
+ *     reproducible bit for bit); behind row_ptr[s_kv] follow the unused slots in ascending flat order.
+ * s_q * topk must fit in 31 bits.  q_start_index_s has the meaning it has in the backward's parameter block; SMLA_NO_CAUSAL: no causal bound.
+ * `workspace`: device memory, 256-byte aligned, at least smla_index_inverse_workspace_size() bytes (0 = bad shape). */
+size_t smla_index_inverse_workspace_size(int32_t s_q, int32_t topk, int32_t s_kv);
+int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_t s_kv, int32_t q_start_index_s,
+                       int32_t* row_ptr, int32_t* entries, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Synchronises `stream`, reads the device error word in the workspace and returns SMLA_OK or
  * SMLA_ERR_DEVICE_TIMEOUT (or SMLA_ERR_LAUNCH if the stream reports a CUDA error). */
 int smla_bwd_status(void* workspace, void* stream);

@@ -17,7 +17,7 @@ LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libsmla_bwd.so")
 
 SOURCES = ["smla_api.cu"]
-HEADERS = ["sm100_ptx.cuh", "smla_kernels.cuh"]
+HEADERS = ["sm100_ptx.cuh", "smla_kernels.cuh", "smla_index_inverse.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

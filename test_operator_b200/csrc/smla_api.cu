@@ -12,6 +12,7 @@
 
 #include "../../include/smla_bwd.h"
 #include "smla_kernels.cuh"
+#include "smla_index_inverse.cuh"
 
 namespace {
 
@@ -469,6 +470,79 @@ int smla_bwd_status(void* workspace, void* stream) {
     if (cudaMemcpyAsync(&flag, workspace, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
     if (cudaStreamSynchronize(st) != cudaSuccess) return SMLA_ERR_LAUNCH;
     return flag == 0 ? SMLA_OK : SMLA_ERR_DEVICE_TIMEOUT;
+}
+
+// ---- index inverse (CSR by kv row) -------------------------------------------------------------
+namespace {
+inline size_t up256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+struct InvLayout { size_t keys_a, keys_b, vals_tmp, hist, totals, total; };
+inline InvLayout inv_layout(int64_t n, const inv::Plan& pl) {
+    InvLayout l;
+    size_t off = 0;
+    l.keys_a = off; off += up256(static_cast<size_t>(n) * 4);
+    l.keys_b = off; off += up256(static_cast<size_t>(n) * 4);
+    l.vals_tmp = off; off += up256(static_cast<size_t>(n) * 4);
+    l.hist = off; off += up256(static_cast<size_t>(inv::kMaxRadix) * pl.n_blocks * 4);
+    l.totals = off; off += up256(inv::kMaxRadix * 4);
+    l.total = off;
+    return l;
+}
+inline bool inv_shape_ok(int32_t s_q, int32_t topk, int32_t s_kv) {
+    return s_q >= 0 && topk > 0 && s_kv > 0 && s_kv < INT32_MAX &&
+           static_cast<int64_t>(s_q) * topk <= static_cast<int64_t>(INT32_MAX);
+}
+}  // namespace
+
+size_t smla_index_inverse_workspace_size(int32_t s_q, int32_t topk, int32_t s_kv) {
+    if (!inv_shape_ok(s_q, topk, s_kv)) return 0;
+    const int64_t n = static_cast<int64_t>(s_q) * topk;
+    return inv_layout(n, inv::make_plan(n, s_kv)).total + 256;
+}
+
+int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_t s_kv, int32_t q_start_index_s,
+                       int32_t* row_ptr, int32_t* entries, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!inv_shape_ok(s_q, topk, s_kv) || !row_ptr) return SMLA_ERR_BAD_ARG;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t n = static_cast<int64_t>(s_q) * topk;
+    g_last_launches = 0;
+    if (n == 0) {
+        if (cudaMemsetAsync(row_ptr, 0, (static_cast<size_t>(s_kv) + 1) * 4, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
+        return SMLA_OK;
+    }
+    if (!indices || !entries || !workspace) return SMLA_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SMLA_ERR_BAD_ARG;
+    const inv::Plan pl = inv::make_plan(n, s_kv);
+    const InvLayout l = inv_layout(n, pl);
+    if (workspace_bytes < l.total) return SMLA_ERR_WORKSPACE;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    uint32_t* kbuf[2] = {reinterpret_cast<uint32_t*>(ws + l.keys_a), reinterpret_cast<uint32_t*>(ws + l.keys_b)};
+    int32_t* vtmp = reinterpret_cast<int32_t*>(ws + l.vals_tmp);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(ws + l.hist);
+    uint32_t* totals = reinterpret_cast<uint32_t*>(ws + l.totals);
+    const uint32_t mask = (1u << pl.digit_bits) - 1u;
+    const int radix = 1 << pl.digit_bits;
+    const int causal = q_start_index_s != SMLA_NO_CAUSAL;
+    int launches = 0;
+    const int32_t* vin = nullptr;
+    for (int pass = 0; pass < pl.passes; ++pass) {
+        const int shift = pass * pl.digit_bits;
+        if (pass == 0)
+            inv::make_keys_kernel<<<pl.n_blocks, inv::kThreads, 0, st>>>(indices, kbuf[0], hist, n, topk, s_kv, causal,
+                                                                         causal ? q_start_index_s : 0, mask, pl.n_blocks);
+        else
+            inv::histogram_kernel<<<pl.n_blocks, inv::kThreads, 0, st>>>(kbuf[pass & 1], hist, n, shift, mask, pl.n_blocks);
+        inv::scan_rows_kernel<<<radix, 1024, 0, st>>>(hist, totals, pl.n_blocks);
+        // the last pass must land in `entries`: passes alternate between the temporary and the output
+        int32_t* vout = ((pl.passes - 1 - pass) & 1) ? vtmp : entries;
+        inv::scatter_kernel<<<pl.n_blocks, inv::kThreads, 0, st>>>(kbuf[pass & 1], vin, kbuf[(pass + 1) & 1], vout, hist,
+                                                                   totals, n, shift, mask, pl.n_blocks);
+        vin = vout;
+        launches += 3;
+    }
+    const int rows = s_kv + 1;
+    inv::row_ptr_kernel<<<(rows + 255) / 256, 256, 0, st>>>(kbuf[pl.passes & 1], row_ptr, n, s_kv);
+    g_last_launches = launches + 1;
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
 }
 
 int smla_bwd_last_launch_count(void) { return g_last_launches; }

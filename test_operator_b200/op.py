@@ -110,6 +110,12 @@ def load_library() -> ctypes.CDLL:
         lib.smla_fwd_run.restype = ctypes.c_int
         lib.smla_fwd_run.argtypes = [ctypes.POINTER(_FwdParams), ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
         lib.smla_bwd_last_launch_count.restype = ctypes.c_int
+        lib.smla_index_inverse_workspace_size.restype = ctypes.c_size_t
+        lib.smla_index_inverse_workspace_size.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+        lib.smla_index_inverse.restype = ctypes.c_int
+        lib.smla_index_inverse.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                           ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_size_t, ctypes.c_void_p]
         lib.smla_bwd_status_string = lib.smla_status_string
         lib.smla_status_string.restype = ctypes.c_char_p
         lib.smla_status_string.argtypes = [ctypes.c_int]
@@ -355,6 +361,31 @@ class SparseMLAFunction(torch.autograd.Function):
 def sparse_mla(q, kv, indices, sm_scale: Optional[float] = None, q_start_index_s: Optional[int] = 0):
     """Differentiable sparse MLA attention (bf16 in, bf16 out; gradients for q and kv)."""
     return SparseMLAFunction.apply(q, kv, indices, sm_scale, q_start_index_s)
+
+
+def index_inverse(indices: torch.Tensor, s_kv: int, q_start_index_s: Optional[int] = None):
+    """CSR by kv row of the valid slots of `indices` [s_q, topk] (or [s_q, 1, topk]) int32 on a CUDA device.
+
+    Returns (row_ptr [s_kv + 1] int32, entries [s_q * topk] int32): `entries[row_ptr[r]:row_ptr[r + 1]]` are the flat
+    slot ids `q * topk + slot` that chose kv row r, ascending; behind `row_ptr[s_kv]` follow the unused slots in
+    ascending flat order.  The order is fixed, so two calls agree bit for bit.  Validity as in the backward
+    (`mla_bwd/mla_bwd.cu:765-789`): `0 <= idx < s_kv`, and `idx <= q_start_index_s + q` unless that is None."""
+    _check(indices.is_cuda and indices.dtype == torch.int32 and indices.is_contiguous(), "indices must be a contiguous CUDA int32 tensor")
+    _check(indices.dim() in (2, 3) and (indices.dim() == 2 or indices.shape[1] == 1), "indices must be [s_q, topk] or [s_q, 1, topk]")
+    s_q, topk = indices.shape[0], indices.shape[-1]
+    lib = load_library()
+    need = lib.smla_index_inverse_workspace_size(s_q, topk, s_kv)
+    _check(need > 0, "unsupported shape (s_kv and topk positive, s_q * topk below 2^31)")
+    with torch.cuda.device(indices.device):
+        ws = torch.empty(need, dtype=torch.uint8, device=indices.device)
+        row_ptr = torch.empty(s_kv + 1, dtype=torch.int32, device=indices.device)
+        entries = torch.empty(s_q * topk, dtype=torch.int32, device=indices.device)
+        st = lib.smla_index_inverse(indices.data_ptr(), s_q, topk, s_kv,
+                                    NO_CAUSAL if q_start_index_s is None else int(q_start_index_s),
+                                    row_ptr.data_ptr(), entries.data_ptr(), ws.data_ptr(), need,
+                                    torch.cuda.current_stream().cuda_stream)
+    _raise_status(lib, st, "smla_index_inverse")
+    return row_ptr, entries
 
 
 def mla_bwd_noalloc(q, kv, dO, lse, O, indices, dQ, dKV, sm_scale: Optional[float] = None,

@@ -132,3 +132,20 @@ def _query_sharded_worker(rank, world, port, q_start):
 def test_query_sharded_reduce_scatter_two_ranks_gloo(q_start):
     port = _free_port()
     mp.spawn(_query_sharded_worker, args=(2, port, q_start), nprocs=2, join=True)
+
+
+def test_index_inverse_oracle_forms_agree_and_abi_rejects_bad_shapes():
+    import numpy as np
+    from oracle.index_inverse_ref import index_inverse_ref, index_inverse_loops
+    g = np.random.default_rng(3)
+    for s_q, topk, s_kv, start in [(5, 8, 13, None), (9, 16, 7, 2), (1, 32, 300, None), (0, 4, 5, None)]:
+        idx = g.integers(-3, s_kv + 3, size=(s_q, topk)).astype(np.int32)
+        a_ptr, a_ent = index_inverse_ref(idx, s_kv, start)
+        b_ptr, b_ent = index_inverse_loops(idx, s_kv, start)
+        assert np.array_equal(a_ptr, b_ptr) and np.array_equal(a_ent, b_ent)
+    lib = op.load_library()
+    assert lib.smla_index_inverse_workspace_size(4096, 2048, 32768) >= 3 * 4096 * 2048 * 4
+    assert lib.smla_index_inverse_workspace_size(4, 0, 10) == 0
+    assert lib.smla_index_inverse_workspace_size(1 << 20, 1 << 12, 10) == 0      # s_q * topk needs more than 31 bits
+    assert lib.smla_index_inverse(None, 4, 32, 0, 0, None, None, None, 0, None) == 1
+    assert lib.smla_index_inverse(None, 4, 32, 10, 0, None, None, None, 0, None) == 1
