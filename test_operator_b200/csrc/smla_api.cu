@@ -514,6 +514,9 @@ int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_
     const inv::Plan pl = inv::make_plan(n, s_kv);
     const InvLayout l = inv_layout(n, pl);
     if (workspace_bytes < l.total) return SMLA_ERR_WORKSPACE;
+    if (cudaFuncSetAttribute(inv::scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, inv::kScatterDynSmem) !=
+        cudaSuccess)
+        return SMLA_ERR_LAUNCH;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     uint32_t* kbuf[2] = {reinterpret_cast<uint32_t*>(ws + l.keys_a), reinterpret_cast<uint32_t*>(ws + l.keys_b)};
     int32_t* vtmp = reinterpret_cast<int32_t*>(ws + l.vals_tmp);
@@ -534,7 +537,7 @@ int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_
         inv::scan_rows_kernel<<<radix, 1024, 0, st>>>(hist, totals, pl.n_blocks);
         // the last pass must land in `entries`: passes alternate between the temporary and the output
         int32_t* vout = ((pl.passes - 1 - pass) & 1) ? vtmp : entries;
-        inv::scatter_kernel<<<pl.n_blocks, inv::kThreads, 0, st>>>(kbuf[pass & 1], vin, kbuf[(pass + 1) & 1], vout, hist,
+        inv::scatter_kernel<<<pl.n_blocks, inv::kThreads, inv::kScatterDynSmem, st>>>(kbuf[pass & 1], vin, kbuf[(pass + 1) & 1], vout, hist,
                                                                    totals, n, shift, mask, pl.n_blocks);
         vin = vout;
         launches += 3;

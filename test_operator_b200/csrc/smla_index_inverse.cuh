@@ -128,58 +128,112 @@ scan_rows_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ totals, int
     if (threadIdx.x == 0) totals[blockIdx.x] = carry;
 }
 
-// Stable scatter of one pass.  A block walks its contiguous range tile by tile (kThreads entries, thread id order =
-// flat order).  Inside a tile the rank of an entry among the entries with the same digit is: entries of earlier
-// tiles (running digit base) + entries of earlier warps (per-warp counts, prefixed) + earlier lanes of the own warp
-// (match mask).  vals_in == nullptr means the values are the flat positions themselves (first pass).
+// Stable scatter of one pass.  Warp w of a block owns the contiguous entries [w * kWarpItems, (w + 1) * kWarpItems)
+// of the block's range, so (warp, step, lane) order is flat order.
+//   1. every warp counts the digits of its entries (private shared-memory counters);
+//   2. the counts are prefixed over the warps and over the digits: block-local position of every (digit, warp) run;
+//   3. every warp places its entries, step by step, into a shared-memory copy of the block's output in digit order
+//      (position = running base of (warp, digit) + rank among the lanes of the step with the same digit);
+//   4. the staged entries go out in that order: entry j of digit d lands at global base of (d, block) + j - local
+//      base of d, so consecutive threads write consecutive addresses inside a digit's run (about kBlockItems / radix
+//      entries) instead of 32 different lines per warp instruction.
+// vals_in == nullptr means the values are the flat positions themselves (first pass).
+constexpr int kScatterDynSmem = kBlockItems * 8;   // staged keys + values
+
+// Lanes of the warp whose digit (below 256) equals this lane's, among the active lanes.  Eight ballots: the
+// `match.any` instruction gives the same mask but runs on a pipe that takes a warp every ~64 cycles per SM, which
+// bounded the whole sort (70 % pipe utilisation under ncu) when it was used.
+__device__ __forceinline__ uint32_t same_digit_lanes(uint32_t d, bool active) {
+    uint32_t peers = __ballot_sync(0xffffffffu, active);
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        const bool bit = (d >> b) & 1u;
+        const uint32_t m = __ballot_sync(0xffffffffu, bit);
+        peers &= bit ? m : ~m;
+    }
+    return peers;
+}
+
 __global__ void __launch_bounds__(kThreads)
 scatter_kernel(const uint32_t* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
                uint32_t* __restrict__ keys_out, int32_t* __restrict__ vals_out, const uint32_t* __restrict__ hist,
                const uint32_t* __restrict__ totals, int64_t n, int shift, uint32_t mask, int n_blocks) {
-    __shared__ uint32_t digit_base[kMaxRadix];
+    constexpr int kWarpItems = kBlockItems / kWarps;   // 512
+    constexpr int kSteps = kWarpItems / 32;            // 16
+    extern __shared__ __align__(16) uint32_t staged[];
+    uint32_t* skeys = staged;
+    int32_t* svals = reinterpret_cast<int32_t*>(staged + kBlockItems);
+    __shared__ uint32_t global_base[kMaxRadix];   // first output position of (digit, this block)
+    __shared__ uint32_t local_base[kMaxRadix];    // first staged position of the digit
     __shared__ uint32_t warp_count[kWarps][kMaxRadix];
     __shared__ uint32_t warp_sums[32];
     __shared__ uint32_t total;
     const int radix = static_cast<int>(mask) + 1;
+    for (int i = threadIdx.x; i < kWarps * kMaxRadix; i += kThreads) (&warp_count[0][0])[i] = 0;
     {
         // exclusive prefix of the digit totals (radix <= 256 <= kThreads: one value per thread)
         const uint32_t t = threadIdx.x < radix ? totals[threadIdx.x] : 0u;
         const uint32_t ex = block_exclusive_scan(t, warp_sums, &total);
-        if (threadIdx.x < radix) digit_base[threadIdx.x] = ex + hist[static_cast<size_t>(threadIdx.x) * n_blocks + blockIdx.x];
+        if (threadIdx.x < radix) global_base[threadIdx.x] = ex + hist[static_cast<size_t>(threadIdx.x) * n_blocks + blockIdx.x];
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t lanes_below = (1u << lane) - 1u;
-    const int64_t base = static_cast<int64_t>(blockIdx.x) * kBlockItems;
-    for (int t = 0; t < kItems; ++t) {
-        const int64_t tile0 = base + static_cast<int64_t>(t) * kThreads;
-        if (tile0 >= n) break;   // uniform over the block
-        for (int i = threadIdx.x; i < kWarps * kMaxRadix; i += kThreads) (&warp_count[0][0])[i] = 0;
-        __syncthreads();
-        const int64_t i = tile0 + threadIdx.x;
+    const int64_t block0 = static_cast<int64_t>(blockIdx.x) * kBlockItems;
+    const int64_t first = block0 + static_cast<int64_t>(warp) * kWarpItems + lane;
+    uint32_t* mine = warp_count[warp];
+#pragma unroll 4
+    for (int t = 0; t < kSteps; ++t) {
+        const int64_t i = first + t * 32;
         const bool active = i < n;
-        uint32_t key = 0, d = 0xffffffffu;
-        if (active) { key = keys_in[i]; d = digit_of(key, shift, mask); }
-        const uint32_t peers = __match_any_sync(0xffffffffu, d);
-        const uint32_t rank_in_warp = __popc(peers & lanes_below);
-        if (active && rank_in_warp == 0) warp_count[warp][d] = __popc(peers);
-        __syncthreads();
+        if (active) atomicAdd(&mine[digit_of(keys_in[i], shift, mask)], 1u);   // counts only: order does not matter
+    }
+    __syncthreads();
+    {
+        // per digit: counts of the warps -> offsets inside the digit's run; the run lengths -> local bases
+        uint32_t run = 0;
         if (threadIdx.x < radix) {
-            uint32_t run = digit_base[threadIdx.x];
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
                 const uint32_t c = warp_count[w][threadIdx.x];
                 warp_count[w][threadIdx.x] = run;
                 run += c;
             }
-            digit_base[threadIdx.x] = run;
         }
-        __syncthreads();
+        const uint32_t lb = block_exclusive_scan(run, warp_sums, &total);
+        if (threadIdx.x < radix) {
+            local_base[threadIdx.x] = lb;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) warp_count[w][threadIdx.x] += lb;
+        }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int t = 0; t < kSteps; ++t) {
+        const int64_t i = first + t * 32;
+        const bool active = i < n;
+        const uint32_t key = active ? keys_in[i] : 0u;   // second read of the warp's 2 KB: served by L1 / L2
+        const uint32_t d = active ? digit_of(key, shift, mask) : 0u;
+        const uint32_t peers = same_digit_lanes(d, active);
+        const uint32_t rank = __popc(peers & lanes_below);
+        uint32_t pos = 0;
+        if (active) pos = mine[d] + rank;
+        __syncwarp();
+        if (active && rank == 0) mine[d] += __popc(peers);
+        __syncwarp();
         if (active) {
-            const uint32_t pos = warp_count[warp][d] + rank_in_warp;
-            keys_out[pos] = key;
-            vals_out[pos] = vals_in ? vals_in[i] : static_cast<int32_t>(i);
+            skeys[pos] = key;
+            svals[pos] = vals_in ? vals_in[i] : static_cast<int32_t>(i);
         }
-        __syncthreads();
+    }
+    __syncthreads();
+    const int64_t left = n - block0;
+    const int count = left < kBlockItems ? static_cast<int>(left) : kBlockItems;
+    for (int j = threadIdx.x; j < count; j += kThreads) {
+        const uint32_t key = skeys[j];
+        const uint32_t d = digit_of(key, shift, mask);
+        const uint32_t pos = global_base[d] + (static_cast<uint32_t>(j) - local_base[d]);
+        keys_out[pos] = key;
+        vals_out[pos] = svals[j];
     }
 }
 
