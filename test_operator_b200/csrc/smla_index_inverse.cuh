@@ -154,7 +154,7 @@ __device__ __forceinline__ uint32_t same_digit_lanes(uint32_t d, bool active) {
     return peers;
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 scatter_kernel(const uint32_t* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
                uint32_t* __restrict__ keys_out, int32_t* __restrict__ vals_out, const uint32_t* __restrict__ hist,
                const uint32_t* __restrict__ totals, int64_t n, int shift, uint32_t mask, int n_blocks) {
@@ -181,7 +181,7 @@ scatter_kernel(const uint32_t* __restrict__ keys_in, const int32_t* __restrict__
     const int64_t block0 = static_cast<int64_t>(blockIdx.x) * kBlockItems;
     const int64_t first = block0 + static_cast<int64_t>(warp) * kWarpItems + lane;
     uint32_t* mine = warp_count[warp];
-#pragma unroll 4
+#pragma unroll
     for (int t = 0; t < kSteps; ++t) {
         const int64_t i = first + t * 32;
         const bool active = i < n;
@@ -207,11 +207,20 @@ scatter_kernel(const uint32_t* __restrict__ keys_in, const int32_t* __restrict__
         }
     }
     __syncthreads();
-#pragma unroll 4
+    // second read of the warp's 2 KB of keys (L1 / L2), all of it in flight before the dependent ranking starts
+    uint32_t keys[kSteps];
+    int32_t vals[kSteps];
+#pragma unroll
+    for (int t = 0; t < kSteps; ++t) {
+        const int64_t i = first + t * 32;
+        keys[t] = i < n ? keys_in[i] : 0u;
+        vals[t] = (vals_in && i < n) ? vals_in[i] : static_cast<int32_t>(i);
+    }
+#pragma unroll
     for (int t = 0; t < kSteps; ++t) {
         const int64_t i = first + t * 32;
         const bool active = i < n;
-        const uint32_t key = active ? keys_in[i] : 0u;   // second read of the warp's 2 KB: served by L1 / L2
+        const uint32_t key = keys[t];
         const uint32_t d = active ? digit_of(key, shift, mask) : 0u;
         const uint32_t peers = same_digit_lanes(d, active);
         const uint32_t rank = __popc(peers & lanes_below);
@@ -222,12 +231,13 @@ scatter_kernel(const uint32_t* __restrict__ keys_in, const int32_t* __restrict__
         __syncwarp();
         if (active) {
             skeys[pos] = key;
-            svals[pos] = vals_in ? vals_in[i] : static_cast<int32_t>(i);
+            svals[pos] = vals[t];
         }
     }
     __syncthreads();
     const int64_t left = n - block0;
     const int count = left < kBlockItems ? static_cast<int>(left) : kBlockItems;
+#pragma unroll 4
     for (int j = threadIdx.x; j < count; j += kThreads) {
         const uint32_t key = skeys[j];
         const uint32_t d = digit_of(key, shift, mask);
