@@ -57,6 +57,14 @@ typedef struct smla_bwd_params {
     int32_t q_start_index_s; /* slot valid only if idx <= q_start_index_s + query row (reference uses 0,
                                 mla_bwd.cu:122,772); SMLA_NO_CAUSAL disables the bound */
     int32_t lse_is_base2;    /* 1: lse in base-2 units as the reference operator expects (mla_bwd.cu:262-270); 0: natural log */
+    /* Optional (null: one sequence, every slot in use): i32 [s_q][4], 16-byte aligned, per query
+     *   {first kv row of the query's sequence, kv rows of that sequence, position for the causal rule, top-k slots in use}.
+     * Index values are then relative to the sequence's first row and valid in [0, rows of the sequence); slot j of a
+     * query takes part only if j < slots in use; with the causal rule on, only if idx <= position (q_start_index_s
+     * then only switches the rule on or off).  s_kv stays the total number of kv / dKV rows.  This is how packed
+     * (variable-length) and batched inputs run as one launch chain; the fields follow the per-query ones of the
+     * reference's richer parameter block (dq_test/dq_phase_capture.cuh:107-109). */
+    const int32_t* query_meta;
 } smla_bwd_params;
 
 /* Workspace (device memory) needed for `p`, never more than about `budget_bytes` when that is
@@ -90,8 +98,8 @@ int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t worksp
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
  *    device current) and caches it; make that first call before any stream capture begins.
  *  - All calls on a device share the one array.  It keeps whatever the previous call left; every byte that
- *    is read is rewritten first (the error word is cleared, Delta and the S/dS rows of a pass are fully
- *    overwritten before use).  Two calls whose kernels overlap on the GPU (different streams, or threads)
+ *    is read is rewritten first (Delta and the S/dS rows of a pass are fully overwritten before use; the
+ *    error word starts at zero with the library image and is cleared again when a timeout has been reported).  Two calls whose kernels overlap on the GPU (different streams, or threads)
  *    race on it: serialise them.
  *  - Status of the last call: smla_bwd_noalloc_status(stream) (synchronises the stream). */
 int smla_bwd_run_noalloc(const smla_bwd_params* p, void* stream);
@@ -112,6 +120,7 @@ typedef struct smla_fwd_params {
     float sm_scale;          /* <= 0 selects 1/sqrt(576) */
     int32_t q_start_index_s; /* as in smla_bwd_params */
     int32_t lse_is_base2;    /* 1: write lse in base-2 units (what smla_bwd_run expects by default); 0: natural log */
+    const int32_t* query_meta; /* as in smla_bwd_params */
 } smla_fwd_params;
 size_t smla_fwd_workspace_size(const smla_fwd_params* p, size_t budget_bytes);
 int smla_fwd_run(const smla_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
@@ -141,9 +150,36 @@ size_t smla_index_inverse_workspace_size(int32_t s_q, int32_t topk, int32_t s_kv
 int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_t s_kv, int32_t q_start_index_s,
                        int32_t* row_ptr, int32_t* entries, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The first 256 bytes of a workspace hold the device error word.  Clear them once before the workspace's first
+ * use (this call, or any memset); the run entry points do not, so that a timeout recorded by any call of a
+ * sequence is still there when the status is read. */
+int smla_bwd_workspace_init(void* workspace, void* stream);
+
 /* Synchronises `stream`, reads the device error word in the workspace and returns SMLA_OK or
- * SMLA_ERR_DEVICE_TIMEOUT (or SMLA_ERR_LAUNCH if the stream reports a CUDA error). */
+ * SMLA_ERR_DEVICE_TIMEOUT (or SMLA_ERR_LAUNCH if the stream reports a CUDA error).  A recorded timeout is
+ * reported once: the word is cleared on the way out.  The reference swallows device-side failures
+ * (mla_bwd/mla_bwd.cu:814-818,965-968); this is the replacement. */
 int smla_bwd_status(void* workspace, void* stream);
+/* The raw word the last smla_bwd_status on this thread read: 0, or 100 * kernel + the site of the wait that gave up. */
+int smla_bwd_last_device_code(void);
+
+/* How one pass of the backward is scheduled.  chunks = 0: the kernels one after another on the caller's stream.
+ * chunks >= 2: the queries of a pass are cut into that many parts and the dKV kernel of a part runs on a second
+ * stream owned by the library, on `dkv_pairs` 2-SM clusters, beside the recompute and dQ kernels of the next part
+ * (the dKV kernel is bound by the chip's fp32 reduction rate, not by its SMs).  The second stream and its events
+ * are created by the first call that needs them on a device: make that call before a stream capture begins.
+ * Process-wide; the environment variable SMLA_SCHEDULE="chunks,dkv_pairs" sets the initial value. */
+int smla_bwd_set_schedule(int chunks, int dkv_pairs);
+void smla_bwd_get_schedule(int* chunks, int* dkv_pairs);
+
+/* Test hooks for the bounded waits inside the kernels (every wait on a barrier or a flag gives up after a limit,
+ * records a code and lets the kernel return).  smla_debug_set_wait_limit_cycles changes the limit for later
+ * launches (<= 0 restores the default of about a second).  smla_selftest_wait_timeout launches a one-warp kernel
+ * that waits, with the given limit, on something nothing ever signals (which = 0: sleeping barrier wait, 1:
+ * spinning barrier wait, 2: counter wait) and writes {first wait returned, second wait returned, cycles waited}
+ * to out3 (device memory, 3 x int64); the code 900 + 10 * which lands in the workspace's error word. */
+int smla_debug_set_wait_limit_cycles(long long cycles);
+int smla_selftest_wait_timeout(void* workspace, int which, long long limit_cycles, long long* out3, void* stream);
 
 /* Number of kernels (own kernels, memset excluded) the last smla_bwd_run_stages on this thread launched. */
 int smla_bwd_last_launch_count(void);

@@ -1,4 +1,4 @@
-"""CPU oracle for the sparse MLA attention backward. TEST INFRASTRUCTURE ONLY.
+"""Oracle for the sparse MLA attention backward. TEST INFRASTRUCTURE ONLY.
 
 This file restates, in plain fp32 PyTorch, the algorithm of the reference's own checker
 (`mla_bwd/test_mla_bwd.py:18-90`, function `build_reference`) and of the forward used to
@@ -10,6 +10,11 @@ Parity pinning: the reference stores no golden vectors for this path (every test
 regenerates seeded random inputs).  The restatement is therefore pinned against outputs
 of the reference function itself, executed on CPU tensors by
 `tests/golden/make_golden.py`; the resulting vectors live in `tests/golden/*.npz`.
+
+The functions are plain torch and run on whatever device their inputs live on: on CPU tensors they
+are the CPU oracle (and the timed CPU baseline); on CUDA tensors the same fp32 arithmetic runs in
+torch's own kernels, which lets the tests check every query of the full-size workloads in seconds,
+as the reference's own script does (`mla_bwd/test_mla_bwd.py:93-112` builds its reference on the GPU).
 
 Math contract (identical in the CUDA path):
     P      = Q . K_g^T                                  (K_g = kv rows gathered by `indices`)
@@ -42,7 +47,7 @@ def valid_mask(indices: torch.Tensor, s_kv: int, q_start_index_s: Optional[int])
     """
     ok = (indices >= 0) & (indices < s_kv)
     if q_start_index_s is not None:
-        pos = q_start_index_s + torch.arange(indices.shape[0], dtype=torch.int64).unsqueeze(1)
+        pos = q_start_index_s + torch.arange(indices.shape[0], dtype=torch.int64, device=indices.device).unsqueeze(1)
         ok = ok & (indices.to(torch.int64) <= pos)
     return ok
 
@@ -68,16 +73,19 @@ def sparse_mla_fwd_ref(
     kf = kv.float()
     safe = indices.clamp(0, s_kv - 1).long()
     ok = valid_mask(indices, s_kv, q_start_index_s)
-    o = torch.empty(s_q, h_q, d_v, dtype=torch.bfloat16)
-    lse = torch.empty(s_q, h_q, dtype=torch.float32)
+    dev = q.device
+    o = torch.empty(s_q, h_q, d_v, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(s_q, h_q, dtype=torch.float32, device=dev)
+    neg_inf = torch.tensor(float("-inf"), device=dev)
+    pos_inf = torch.tensor(float("inf"), device=dev)
     for s0 in range(0, s_q, chunk_s):
         s1 = min(s0 + chunk_s, s_q)
         kg = kf.index_select(0, safe[s0:s1].reshape(-1)).view(s1 - s0, -1, d_qk)
         p = torch.matmul(q[s0:s1].float(), kg.transpose(-2, -1))
-        p = torch.where(ok[s0:s1].unsqueeze(1), p, torch.tensor(float("-inf")))
+        p = torch.where(ok[s0:s1].unsqueeze(1), p, neg_inf)
         logits = p * scale
         l = torch.logsumexp(logits, dim=-1)
-        l = torch.where(torch.isinf(l) & (l < 0), torch.tensor(float("inf")), l)
+        l = torch.where(torch.isinf(l) & (l < 0), pos_inf, l)
         s = torch.exp(logits - l.unsqueeze(-1))
         o[s0:s1] = torch.matmul(s, kg[..., :d_v]).to(torch.bfloat16)
         lse[s0:s1] = l
@@ -118,14 +126,15 @@ def sparse_mla_bwd_ref(
     safe = indices.clamp(0, s_kv - 1).long()
     ok = valid_mask(indices, s_kv, q_start_index_s)
 
-    dQ = torch.empty(s_q, h_q, d_qk, dtype=torch.float32)
-    dKV = torch.zeros(s_kv, d_qk, dtype=torch.float32)
+    dev = q.device
+    dQ = torch.empty(s_q, h_q, d_qk, dtype=torch.float32, device=dev)
+    dKV = torch.zeros(s_kv, d_qk, dtype=torch.float32, device=dev)
     if return_intermediates:
-        delta_all = torch.empty(s_q, h_q, dtype=torch.float32)
-        S_all = torch.empty(s_q, topk, h_q, dtype=torch.bfloat16)
-        dS_all = torch.empty(s_q, topk, h_q, dtype=torch.bfloat16)
+        delta_all = torch.empty(s_q, h_q, dtype=torch.float32, device=dev)
+        S_all = torch.empty(s_q, topk, h_q, dtype=torch.bfloat16, device=dev)
+        dS_all = torch.empty(s_q, topk, h_q, dtype=torch.bfloat16, device=dev)
 
-    neg_inf = torch.tensor(float("-inf"))
+    neg_inf = torch.tensor(float("-inf"), device=dev)
     for s0 in range(0, s_q, chunk_s):
         s1 = min(s0 + chunk_s, s_q)
         cs = s1 - s0

@@ -1,4 +1,4 @@
-// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (tiled and gather4), tcgen05 (TMEM
+// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (tiled loads, bulk stores), cp.async, tcgen05 (TMEM
 // allocation, UMMA issue/commit, TMEM loads) and the shared-memory / instruction descriptors
 // the UMMA unit consumes.  Everything here is device-only and header-only.
 #pragma once
@@ -9,15 +9,25 @@ namespace smla {
 
 // ---------------------------------------------------------------------------------------------
 // Error reporting for bounded waits.  A wait that runs out publishes a code in global memory
-// and raises a CTA-wide abort flag in shared memory; every later wait in the CTA returns at
-// once, so the kernel drains and exits instead of hanging the device.
+// and raises a CTA-wide abort flag in shared memory (and in the partner CTA of a 2-CTA cluster);
+// every later wait in the CTA returns at once, so the kernel drains and exits instead of
+// hanging the device.
 // ---------------------------------------------------------------------------------------------
 struct WaitCtx {
-    int* g_err;             // global error word (0 = ok)
+    int* g_err;             // global error word (0 = ok; the first code recorded stays)
     volatile int* s_abort;  // CTA-local abort flag in shared memory
+    long long limit;        // cycles a wait may take before it gives up
+    uint32_t peer_abort;    // shared::cluster address of the partner CTA's abort flag, 0 if there is none
 };
 
-constexpr long long kWaitLimitCycles = 2000000000LL;  // ~1 s at B200 clocks
+constexpr long long kWaitLimitCycles = 2000000000LL;  // default limit: ~1 s at B200 clocks
+
+// Give up: flag this CTA and its partner, record the code (the first one wins).
+__device__ __forceinline__ void wait_give_up(const WaitCtx& ctx, int code) {
+    *ctx.s_abort = 1;
+    if (ctx.peer_abort) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ctx.peer_abort), "r"(1) : "memory");
+    atomicCAS(ctx.g_err, 0, code);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -64,9 +74,8 @@ __device__ __noinline__ bool mbar_spin_slow(uint32_t bar, uint32_t parity, const
         if (mbar_test_wait(bar, parity)) return true;
         if ((++it & 255) == 0) {
             if (*ctx.s_abort) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *ctx.s_abort = 1;
-                atomicCAS(ctx.g_err, 0, code);
+            if (clock64() - t0 > ctx.limit) {
+                wait_give_up(ctx, code);
                 return false;
             }
         }
@@ -88,9 +97,8 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const
         if (sleep_ns) __nanosleep(sleep_ns);
         if ((++it & 31) == 0) {
             if (*ctx.s_abort) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *ctx.s_abort = 1;
-                atomicCAS(ctx.g_err, 0, code);
+            if (clock64() - t0 > ctx.limit) {
+                wait_give_up(ctx, code);
                 return false;
             }
         }
@@ -100,6 +108,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
                                           unsigned sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, ctx, code, sleep_ns);
+}
+
+// Wait used only while a CTA winds down after an abort: ignores the abort flag, still bounded.
+__device__ __noinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity, long long limit) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(64);
+        if (clock64() - t0 > limit) return;
+    }
 }
 
 // ---- plain shared-memory counter as a hand-over between two threads of a CTA ------------------------------
@@ -120,9 +137,8 @@ __device__ __noinline__ bool flag_wait_slow(uint32_t saddr, uint32_t want, const
         if (static_cast<int32_t>(flag_load(saddr) - want) >= 0) return true;
         if ((++it & 255) == 0) {
             if (*ctx.s_abort) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *ctx.s_abort = 1;
-                atomicCAS(ctx.g_err, 0, code);
+            if (clock64() - t0 > ctx.limit) {
+                wait_give_up(ctx, code);
                 return false;
             }
         }
@@ -197,6 +213,7 @@ __device__ __forceinline__ void cp_async16_zfill_hint(uint32_t dst, const void* 
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -359,6 +376,17 @@ __device__ __forceinline__ void red_add_f32_if_row(float* addr, float v, int row
         "setp.ge.s32 p, %2, 0;\n\t"
         "@p red.global.add.f32 [%0], %1;\n\t}"
         ::"l"(addr), "f"(v), "r"(row)
+        : "memory");
+}
+
+// The same with an L2 eviction policy: the accumulator rows are touched again by later queries and should
+// outlive the operands that only stream through.
+__device__ __forceinline__ void red_add_f32_if_row_hint(float* addr, float v, int row, uint64_t policy) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ge.s32 p, %2, 0;\n\t"
+        "@p red.global.add.L2::cache_hint.f32 [%0], %1, %3;\n\t}"
+        ::"l"(addr), "f"(v), "r"(row), "l"(policy)
         : "memory");
 }
 

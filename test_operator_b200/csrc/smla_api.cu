@@ -3,11 +3,13 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <climits>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <cstdlib>
+#include <map>
 #include <mutex>
 
 #include "../../include/smla_bwd.h"
@@ -24,6 +26,67 @@ constexpr size_t kDefaultBudget = size_t(6) << 30;  // scratch budget when the c
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 thread_local int g_last_launches = 0;
+thread_local int g_last_device_code = 0;
+
+// ---- schedule of one backward pass ------------------------------------------------------------------------
+// chunks == 0: the four kernels one after another on the caller's stream.
+// chunks >= 2: the queries of a pass are cut into `chunks` parts; recompute and dq of part c run on the caller's
+//   stream while the dkv kernel of part c - 1 runs on a second (internal, higher-priority) stream with a grid of
+//   `dkv_pairs` clusters, the recompute kernels taking the remaining clusters.  The dkv kernel is bound by the
+//   chip's fp32 reduction rate, not by its SMs, so it loses little on fewer SMs, and the SMs it leaves do the
+//   tensor-core work of the other two kernels meanwhile.
+constexpr int kMaxChunks = 16;
+std::atomic<int> g_sched_chunks{-1};      // -1: not yet read from the environment
+std::atomic<int> g_sched_dkv_pairs{0};
+constexpr int kDefaultChunks = 0;
+constexpr int kDefaultDkvPairs = 0;
+std::atomic<long long> g_wait_limit{smla::kWaitLimitCycles};
+
+void schedule(int* chunks, int* dkv_pairs) {
+    int c = g_sched_chunks.load();
+    if (c < 0) {
+        int cc = kDefaultChunks, dp = kDefaultDkvPairs;
+        if (const char* e = std::getenv("SMLA_SCHEDULE")) {      // "chunks,dkv_pairs"
+            int a = 0, b = 0;
+            if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 0 && a <= kMaxChunks && b >= 0) {
+                cc = a;
+                dp = b;
+            }
+        }
+        g_sched_dkv_pairs.store(dp);
+        g_sched_chunks.store(cc);
+        c = cc;
+    }
+    *chunks = c;
+    *dkv_pairs = g_sched_dkv_pairs.load();
+}
+
+// Second stream and the events that order it against the caller's stream, one set per device, created on the first
+// call that needs them.  The mutex is held while a call enqueues, so that two host threads do not interleave their
+// records and waits on the shared events.
+struct DevSched {
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_part[kMaxChunks] = {};
+    bool ready = false;
+};
+std::mutex g_dev_sched_mutex;
+DevSched g_dev_sched[64];
+
+DevSched* dev_sched_locked() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    DevSched& d = g_dev_sched[dev];
+    if (d.ready) return &d;
+    int lo = 0, hi = 0;
+    if (cudaDeviceGetStreamPriorityRange(&lo, &hi) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithPriority(&d.side, cudaStreamNonBlocking, hi) != cudaSuccess) return nullptr;
+    bool ok = cudaEventCreateWithFlags(&d.ev_fork, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&d.ev_join, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < kMaxChunks && ok; ++i) ok = cudaEventCreateWithFlags(&d.ev_part[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) return nullptr;
+    d.ready = true;
+    return &d;
+}
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point: no link-time libcuda dependency,
 // so the library also loads on a machine without a driver (symbol checks on a CPU-only box).
@@ -88,6 +151,7 @@ bool check_params(const smla_bwd_params* p) {
     if (p->h_q <= 0 || p->h_q > 128 || (p->h_q % 8) != 0) return false;
     // int32 row coordinates in the TMA descriptors
     if (static_cast<long long>(p->s_q) * p->h_q > INT_MAX) return false;
+    if (reinterpret_cast<uintptr_t>(p->query_meta) & 15) return false;
     return true;
 }
 
@@ -134,15 +198,18 @@ bool set_smem(K kernel, int bytes) {
 }
 
 // How many 2-CTA clusters of `kernel` the current device runs at once: the grid of a persistent kernel.  A
-// cluster needs two free SMs of one GPC, so this can be less than half the SM count.  Looked up once per device.
+// cluster needs two free SMs of one GPC, so this can be less than half the SM count.  Looked up once per
+// (kernel, device).
 template <typename K>
 int resident_pairs(K kernel, int threads, int smem_bytes) {
     static std::mutex mu;
-    static int cached[64];
+    static std::map<std::pair<const void*, int>, int> cache;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+    const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), dev);
     std::lock_guard<std::mutex> lock(mu);
-    if (cached[dev] > 0) return cached[dev];
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
     int n = 0;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -161,12 +228,12 @@ int resident_pairs(K kernel, int threads, int smem_bytes) {
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return 0;
         n = sms / 2;
     }
-    cached[dev] = n;
+    cache[key] = n;
     return n;
 }
 
 template <int HP>
-int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages) {
+int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages, bool allow_overlap) {
     using namespace smla;
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
     __nv_bfloat16* ds_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.ds_off);
@@ -212,32 +279,72 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
     kp.q_start = kp.causal ? p->q_start_index_s : 0;
 
+    kp.qmeta = reinterpret_cast<const int4*>(p->query_meta);
+    kp.wait_limit = g_wait_limit.load();
+
     if (stages & SMLA_STAGE_DELTA) {
         const int n_rows = p->s_q * p->h_q;
         smla_delta_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(reinterpret_cast<const uint4*>(p->O),
                                                           reinterpret_cast<const uint4*>(p->dO), delta, n_rows);
         ++g_last_launches;
     }
+    const int pairs_r = resident_pairs(smla_recompute_pair_kernel<HP, false>, rp::kThreads, rp::Cfg<HP, false>::kSmemBytes);
+    const int pairs_d = resident_pairs(smla_dkv_pair_kernel<HP>, dp::kThreads, dp::Cfg<HP>::kSmemBytes);
+    if (pairs_r <= 0 || pairs_d <= 0) return SMLA_ERR_LAUNCH;
+    auto launch_recompute = [&](cudaStream_t s_, int pairs) {
+        smla_recompute_pair_kernel<HP, false><<<2 * (kp.nq < pairs ? kp.nq : pairs), rp::kThreads, rp::Cfg<HP, false>::kSmemBytes, s_>>>(tm_qnh, tm_donh, kp);
+        ++g_last_launches;
+    };
+    auto launch_dkv = [&](cudaStream_t s_, int pairs) {
+        smla_dkv_pair_kernel<HP><<<2 * (kp.nq < pairs ? kp.nq : pairs), dp::kThreads, dp::Cfg<HP>::kSmemBytes, s_>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
+        ++g_last_launches;
+    };
+    auto launch_dq = [&](cudaStream_t s_) {
+        smla_dq_kernel<HP, kSplitChunk, kQChunks><<<kp.nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, s_>>>(tm_ds, kp);
+        ++g_last_launches;
+    };
+
+    int chunks = 0, dkv_pairs = 0;
+    schedule(&chunks, &dkv_pairs);
+    const int all = SMLA_STAGE_RECOMPUTE | SMLA_STAGE_DKV | SMLA_STAGE_DQ;
+    if (!allow_overlap || (stages & all) != all || dkv_pairs <= 0 || dkv_pairs >= pairs_d || dkv_pairs >= pairs_r) chunks = 0;
+
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
-        kp.q0 = q0;
-        kp.nq = nq;
-        if (stages & SMLA_STAGE_RECOMPUTE) {
-            const int pairs = resident_pairs(smla_recompute_pair_kernel<HP, false>, rp::kThreads, rp::Cfg<HP, false>::kSmemBytes);
-            if (pairs <= 0) return SMLA_ERR_LAUNCH;
-            smla_recompute_pair_kernel<HP, false><<<2 * (nq < pairs ? nq : pairs), rp::kThreads, rp::Cfg<HP, false>::kSmemBytes, st>>>(tm_qnh, tm_donh, kp);
-            ++g_last_launches;
+        // a part must keep every cluster of both kernels busy for a few queries, or cutting costs more than it hides
+        int parts = chunks;
+        while (parts >= 2 && nq / parts < 4 * pairs_r) --parts;
+        if (parts < 2) {
+            kp.q0 = q0;
+            kp.nq = nq;
+            kp.scr0 = 0;
+            if (stages & SMLA_STAGE_RECOMPUTE) launch_recompute(st, pairs_r);
+            if (stages & SMLA_STAGE_DKV) launch_dkv(st, pairs_d);
+            if (stages & SMLA_STAGE_DQ) launch_dq(st);
+            continue;
         }
-        if (stages & SMLA_STAGE_DKV) {
-            const int pairs = resident_pairs(smla_dkv_pair_kernel<HP>, dp::kThreads, dp::Cfg<HP>::kSmemBytes);
-            if (pairs <= 0) return SMLA_ERR_LAUNCH;
-            smla_dkv_pair_kernel<HP><<<2 * (nq < pairs ? nq : pairs), dp::kThreads, dp::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
-            ++g_last_launches;
+        std::lock_guard<std::mutex> lock(g_dev_sched_mutex);
+        DevSched* ds = dev_sched_locked();
+        if (!ds) return SMLA_ERR_LAUNCH;
+        // the second stream starts behind everything the caller's stream holds so far (dKV cleared, Delta, the
+        // previous pass's readers of the scratch)
+        if (cudaEventRecord(ds->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(ds->side, ds->ev_fork, 0) != cudaSuccess)
+            return SMLA_ERR_LAUNCH;
+        for (int c = 0; c < parts; ++c) {
+            const int a0 = static_cast<int>(static_cast<long long>(nq) * c / parts);
+            const int a1 = static_cast<int>(static_cast<long long>(nq) * (c + 1) / parts);
+            kp.q0 = q0 + a0;
+            kp.nq = a1 - a0;
+            kp.scr0 = a0;
+            launch_recompute(st, c == 0 ? pairs_r : pairs_r - dkv_pairs);
+            if (cudaEventRecord(ds->ev_part[c], st) != cudaSuccess ||
+                cudaStreamWaitEvent(ds->side, ds->ev_part[c], 0) != cudaSuccess)
+                return SMLA_ERR_LAUNCH;
+            launch_dkv(ds->side, c == parts - 1 ? pairs_d : dkv_pairs);
+            launch_dq(st);
         }
-        if (stages & SMLA_STAGE_DQ) {
-            smla_dq_kernel<HP, kSplitChunk, kQChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_ds, kp);
-            ++g_last_launches;
-        }
+        if (cudaEventRecord(ds->ev_join, ds->side) != cudaSuccess || cudaStreamWaitEvent(st, ds->ev_join, 0) != cudaSuccess)
+            return SMLA_ERR_LAUNCH;
     }
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
 }
@@ -255,6 +362,7 @@ bool check_fwd_params(const smla_fwd_params* p) {
     if (p->s_q <= 0 || p->s_kv <= 0 || p->topk <= 0) return false;
     if (p->h_q <= 0 || p->h_q > 128 || (p->h_q % 8) != 0) return false;
     if (static_cast<long long>(p->s_q) * p->h_q > INT_MAX) return false;
+    if (reinterpret_cast<uintptr_t>(p->query_meta) & 15) return false;
     return true;
 }
 
@@ -325,6 +433,9 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     kp.causal = p->q_start_index_s != SMLA_NO_CAUSAL;
     kp.q_start = kp.causal ? p->q_start_index_s : 0;
     kp.gout = reinterpret_cast<__nv_bfloat16*>(p->o);
+    kp.qmeta = reinterpret_cast<const int4*>(p->query_meta);
+    kp.wait_limit = g_wait_limit.load();
+    kp.scr0 = 0;
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
@@ -388,7 +499,9 @@ int smla_bwd_get_workspace_layout(const smla_bwd_params* p, size_t workspace_byt
     return SMLA_OK;
 }
 
-int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream, int stage_mask) {
+namespace {
+int run_stages_impl(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream, int stage_mask,
+                    bool allow_overlap) {
     g_last_launches = 0;
     if (!check_params(p) || !workspace) return SMLA_ERR_BAD_ARG;
     if (!p->q || !p->kv || !p->dO || !p->lse || !p->O || !p->indices || !p->dQ || !p->dKV) return SMLA_ERR_BAD_ARG;
@@ -400,12 +513,36 @@ int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t worksp
     if (!plan_for_workspace(p, workspace_bytes, &pl)) return SMLA_ERR_WORKSPACE;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-    if (cudaMemsetAsync(ws + pl.err_off, 0, 4, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
     if (stage_mask & SMLA_STAGE_ZERO) {
         if (cudaMemsetAsync(p->dKV, 0, size_t(p->s_kv) * SMLA_D_QK * sizeof(float), st) != cudaSuccess)
             return SMLA_ERR_LAUNCH;
     }
-    return pl.h_pad == 64 ? launch_chain<64>(p, pl, ws, st, stage_mask) : launch_chain<128>(p, pl, ws, st, stage_mask);
+    return pl.h_pad == 64 ? launch_chain<64>(p, pl, ws, st, stage_mask, allow_overlap)
+                          : launch_chain<128>(p, pl, ws, st, stage_mask, allow_overlap);
+}
+}  // namespace
+
+int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream, int stage_mask) {
+    return run_stages_impl(p, workspace, workspace_bytes, stream, stage_mask, true);
+}
+
+int smla_bwd_workspace_init(void* workspace, void* stream) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & (kAlign - 1))) return SMLA_ERR_BAD_ARG;
+    return cudaMemsetAsync(workspace, 0, kAlign, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
+
+int smla_bwd_set_schedule(int chunks, int dkv_pairs) {
+    if (chunks < 0 || chunks > kMaxChunks || chunks == 1 || dkv_pairs < 0) return SMLA_ERR_BAD_ARG;
+    g_sched_dkv_pairs.store(dkv_pairs);
+    g_sched_chunks.store(chunks);
+    return SMLA_OK;
+}
+
+void smla_bwd_get_schedule(int* chunks, int* dkv_pairs) {
+    int c = 0, d = 0;
+    schedule(&c, &d);
+    if (chunks) *chunks = c;
+    if (dkv_pairs) *dkv_pairs = d;
 }
 
 int smla_bwd_run(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
@@ -421,7 +558,8 @@ int smla_bwd_run_noalloc(const smla_bwd_params* p, void* stream) {
     void* ws = nullptr;
     const int st = static_workspace_ptr(&ws);
     if (st != SMLA_OK) return st;
-    return smla_bwd_run_stages(p, ws, kStaticWorkspaceBytes, stream, SMLA_STAGE_ALL);
+    // one stream only: this entry point creates nothing, streams and events included
+    return run_stages_impl(p, ws, kStaticWorkspaceBytes, stream, SMLA_STAGE_ALL, false);
 }
 
 size_t smla_bwd_noalloc_capacity(void) { return kStaticWorkspaceBytes; }
@@ -449,7 +587,6 @@ int smla_fwd_run(const smla_fwd_params* p, void* workspace, size_t workspace_byt
     if (!fwd_plan_for_workspace(p, workspace_bytes, &pl)) return SMLA_ERR_WORKSPACE;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-    if (cudaMemsetAsync(ws + pl.err_off, 0, 4, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
     return pl.h_pad == 64 ? launch_fwd_chain<64>(p, pl, ws, st) : launch_fwd_chain<128>(p, pl, ws, st);
 }
 
@@ -469,7 +606,26 @@ int smla_bwd_status(void* workspace, void* stream) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (cudaMemcpyAsync(&flag, workspace, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return SMLA_ERR_LAUNCH;
     if (cudaStreamSynchronize(st) != cudaSuccess) return SMLA_ERR_LAUNCH;
-    return flag == 0 ? SMLA_OK : SMLA_ERR_DEVICE_TIMEOUT;
+    g_last_device_code = flag;
+    if (flag == 0) return SMLA_OK;
+    // reported once: the word is cleared so that the workspace can be used again
+    if (cudaMemsetAsync(workspace, 0, 4, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) return SMLA_ERR_LAUNCH;
+    return SMLA_ERR_DEVICE_TIMEOUT;
+}
+
+int smla_bwd_last_device_code(void) { return g_last_device_code; }
+
+int smla_debug_set_wait_limit_cycles(long long cycles) {
+    g_wait_limit.store(cycles > 0 ? cycles : smla::kWaitLimitCycles);
+    return SMLA_OK;
+}
+
+int smla_selftest_wait_timeout(void* workspace, int which, long long limit_cycles, long long* out3, void* stream) {
+    if (!workspace || !out3 || which < 0 || which > 2 || limit_cycles <= 0) return SMLA_ERR_BAD_ARG;
+    smla::smla_selftest_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<int*>(workspace), out3, which, limit_cycles, 900 + 10 * which);
+    g_last_launches = 1;
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
 }
 
 // ---- index inverse (CSR by kv row) -------------------------------------------------------------

@@ -8,12 +8,12 @@
 //              S = exp2(P*scale*log2e - lse), dS = S*(dP - Delta)*scale -> bf16 scratch
 //   dkv        dKV^T[d, key] = dO^T S + Q^T dS (tcgen05, d on the M axis), then one coalesced
 //              fp32 reduction per (key, 32 consecutive d) straight from TMEM registers
-//   dq         dQ^T[d, head] = K_g^T dS^T (tcgen05, d on the M axis) accumulated over all keys
+//   dq         dQ[head, d] = dS^T K_g (tcgen05, heads on the M axis, d on N) accumulated over all keys
 //
-// Heads are always on the N or K axis of the MMAs, so h_q = 16 / 64 / 128 use the same code
-// (HP = heads padded to 64 or 128).  All shared-memory operand tiles are 128-byte-swizzled
-// [rows x 64 bf16] chunks written by TMA; a chunk is read K-major or MN-major by choosing the
-// descriptor, never by moving data.
+// Heads are padded to HP = 64 or 128, so h_q = 16 / 64 / 128 use the same code.  Gathered kv rows and
+// Q / dO are held as 128-byte-swizzled [rows x 64 bf16] chunks (kv rows by 16-byte cp.async, Q / dO by
+// TMA); S / dS tiles arrive by TMA in the no-swizzle core-matrix order.  A chunk is read K-major or
+// MN-major by choosing the descriptor, never by moving data.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -35,23 +35,52 @@ struct KParams {
     const int32_t* indices;   // [s_q, topk]
     const float* lse;         // [s_q, h_q]
     const float* delta;       // [s_q, h_q]
-    __nv_bfloat16* s_scr;     // [q_chunk, topk_pad, HP]
-    __nv_bfloat16* ds_scr;    // [q_chunk, topk_pad, HP]
+    __nv_bfloat16* s_scr;     // [q_chunk][HP/8 head blocks][topk_pad keys][8 heads], see scratch_offset
+    __nv_bfloat16* ds_scr;    // likewise
     float* dKV;               // [s_kv, 576]
     __nv_bfloat16* dQ;        // [s_q, h_q, 576]
     // forward only
-    float* logits;            // [q_chunk, topk_pad, HP] base-2 logits, -inf where masked
+    float* logits;            // [q_chunk][topk_pad keys][HP heads] base-2 logits, -inf where masked
     float* lse_out;           // [s_q, h_q]
     float lse_out_mult;       // 1 (base 2) or ln 2 (natural log)
     // dq-style kernel: where the result goes (dQ with pitch 576, or o with pitch 512)
     __nv_bfloat16* gout;      // [s_q, h_q, 576] (dQ) or [s_q, h_q, 512] (o)
     int* g_err;
-    int q0;                   // first query (global row) of this pass
-    int nq;                   // queries in this pass
+    int q0;                   // first query (global row) of this launch
+    int nq;                   // queries in this launch
+    int scr0;                 // scratch row of query q0 (a launch may cover a part of the queries a scratch holds)
     int s_q, s_kv, h_q, topk, topk_pad;
     float sm_scale, scale_log2e, lse_mult;
     int q_start, causal;
+    const int4* qmeta;        // optional per query {first kv row of its sequence, kv rows of its sequence,
+                              // position for the causal rule, top-k slots in use}; null: one sequence
+    long long wait_limit;     // cycles a bounded wait may take
 };
+
+// What a query may attend to: rows [kv_base, kv_base + kv_len) of kv, index values relative to kv_base.
+struct QMeta {
+    int kv_base, kv_len, q_pos, topk_len;
+};
+__device__ __forceinline__ QMeta load_qmeta(const KParams& p, int q_global) {
+    if (p.qmeta) {
+        const int4 m = __ldg(p.qmeta + q_global);
+        return QMeta{m.x, m.y, m.z, m.w};
+    }
+    return QMeta{0, p.s_kv, p.q_start + q_global, p.topk};
+}
+// kv row a slot gathers from, -1 when the index is outside the query's sequence (nothing is read then)
+__device__ __forceinline__ int gather_row(int idx, const QMeta& m, const KParams& p) {
+    const int row = m.kv_base + idx;
+    return (idx >= 0 && idx < m.kv_len && row < p.s_kv) ? row : -1;
+}
+// After a bounded wait has given up: let this thread's own cp.async land and leave in-flight TMA loads (they
+// depend on nothing and complete within microseconds) the time to land before the CTA gives up its shared memory.
+__device__ __forceinline__ void abort_wind_down(volatile int* s_abort) {
+    if (*s_abort) {
+        cp_async_wait_all();
+        for (int i = 0; i < 32; ++i) __nanosleep(1000);
+    }
+}
 
 // S / dS scratch of one query: [HP/8 head blocks][topk_pad keys][8 heads] bf16, i.e. the UMMA core matrices
 // (8 keys x 16 bytes) of the no-swizzle layouts stored one after another.  A warp of the recompute kernel holds 32
@@ -65,8 +94,8 @@ __device__ __forceinline__ size_t scratch_offset(int key, int head, int topk_pad
 // error codes recorded by bounded waits: 100*kernel + site
 enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300 };
 
-__device__ __forceinline__ bool slot_valid(int idx, int q_global, const KParams& p) {
-    return idx >= 0 && idx < p.s_kv && (!p.causal || idx <= p.q_start + q_global);
+__device__ __forceinline__ bool slot_valid(int idx, int key, const QMeta& m, const KParams& p) {
+    return key < m.topk_len && idx >= 0 && idx < m.kv_len && m.kv_base + idx < p.s_kv && (!p.causal || idx <= m.q_pos);
 }
 
 // =============================================================================================
@@ -175,8 +204,9 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 4));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t tok = smem_u32(tmem_slot + 2);           // (even CTA) chunks issued so far, the issuers' hand-over
-    static_assert(8 * (2 * kStages + 2 * kQChunks + 4) + 16 <= 512, "barrier area");
-    const WaitCtx wc{p.g_err, s_abort};
+    const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [2] one per issuer, used only while winding down after an abort
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 4) + 16 + 16 <= 512, "barrier area");
+    const WaitCtx wc{p.g_err, s_abort, p.wait_limit, map_to_cta(smem_u32(tmem_slot + 1), rank ^ 1)};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -193,6 +223,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
             mbar_init(bar_tempty + 8 * i, 16);   // 8 softmax warps in each CTA
+            mbar_init(bar_drain + 8 * i, 1);
         }
         fence_mbar_init();
     }
@@ -223,12 +254,18 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         const uint64_t pol_keep = l2_policy_evict_last();
         // index of slot (tile, row i) of query ql, -1 past the top-k; the loads for the next tile are issued
         // before the current tile's copies so that their latency never stalls the ring
+        // (already translated to the kv row to read, -1: read nothing)
         auto load_idx = [&](int ql, int tile, int (&idx)[4]) {
+            if (ql >= nq) {
+                idx[0] = idx[1] = idx[2] = idx[3] = -1;
+                return;
+            }
+            const QMeta qm = load_qmeta(p, p.q0 + ql);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = tile * kTileKeys + rank * 128 + r0 + 32 * i;
-                idx[i] = (ql < nq && key < p.topk)
-                             ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
+                idx[i] = key < p.topk
+                             ? gather_row(__ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key), qm, p) : -1;
             }
         };
         int idx_next[4];
@@ -244,7 +281,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 uint32_t nb[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const bool in_range = idx_next[i] >= 0 && idx_next[i] < p.s_kv;
+                    const bool in_range = idx_next[i] >= 0;
                     nb[i] = in_range ? 16u : 0u;
                     src[i] = kvb + static_cast<size_t>(in_range ? idx_next[i] : 0) * (kDQK * 2);
                 }
@@ -364,6 +401,10 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         ph ^= 1;
                     }
                 }
+                if (*s_abort) {   // winding down: nothing of this thread's may still be in the tensor pipe at dealloc
+                    umma_commit_2cta_mask(bar_drain + 8 * x, 1);
+                    mbar_wait_drain(bar_drain + 8 * x, 0, p.wait_limit);
+                }
             }
         }
     } else {
@@ -388,6 +429,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         int gt = 0;
         for (int ql = pair; ql < nq; ql += n_pairs) {
             const int qg = p.q0 + ql;
+            const QMeta qm = load_qmeta(p, qg);
             if constexpr (!kFwd) {
                 asm volatile("bar.sync 1, 256;" ::: "memory");      // every softmax warp is done with the previous query
                 if (t < 2 * HP) lse_s[t] = stat_next;              // delta_s follows lse_s
@@ -397,12 +439,12 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
                 const int key = tile * kTileKeys + rank * 128 + row;
                 const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                const bool valid = slot_valid(idx, qg, p);
+                const bool valid = slot_valid(idx, key, qm, p);
                 const int b = gt & 1;
                 mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
                 tc_fence_after_sync();
                 if constexpr (kFwd) {
-                    const size_t off = (static_cast<size_t>(ql) * p.topk_pad + key) * HP + g * NH;
+                    const size_t off = (static_cast<size_t>(p.scr0 + ql) * p.topk_pad + key) * HP + g * NH;
                     // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
                     float* t_out = p.logits + off;
@@ -425,7 +467,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 } else {
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
                     // the 32 lanes hold consecutive keys: 32 x 16 bytes of consecutive addresses per store
-                    const size_t off = static_cast<size_t>(ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
+                    const size_t off = static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
                     __nv_bfloat16* s_out = p.s_scr + off;
                     __nv_bfloat16* ds_out = p.ds_scr + off;
                     const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
@@ -479,6 +521,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             }
         }
     }
+    abort_wind_down(s_abort);
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
@@ -499,7 +542,7 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
     const int qg = p.q0 + ql;
     const int h = threadIdx.x % HP;
     const int sl = threadIdx.x / HP;
-    const float* t_row = p.logits + static_cast<size_t>(ql) * p.topk_pad * HP + h;
+    const float* t_row = p.logits + static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + h;
     __shared__ float m_s[512], l_s[512];
     const float ninf = __int_as_float(0xff800000);
     // sweep 1: max (topk_pad is a multiple of 256, so every thread sees whole batches)
@@ -535,7 +578,7 @@ __global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) 
     const float lse2 = (mm == ninf) ? __int_as_float(0x7f800000) : mm + __log2f(ll);
     if (sl == 0 && h < p.h_q) p.lse_out[static_cast<size_t>(qg) * p.h_q + h] = lse2 * p.lse_out_mult;
     // sweep 3: probabilities
-    __nv_bfloat16* s_q = p.s_scr + static_cast<size_t>(ql) * p.topk_pad * HP;   // head-block-major layout, see scratch_offset
+    __nv_bfloat16* s_q = p.s_scr + static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP;   // head-block-major layout, see scratch_offset
     for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
         float t[kBatch];
 #pragma unroll
@@ -605,10 +648,11 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t bar_resfree = bar_res + 8;                         // 1  all UMMAs of the query finished
     const uint32_t bar_ufull = bar_resfree + 8;                       // [kUnits] accumulator unit complete
     const uint32_t bar_uempty = bar_ufull + 8 * kUnits;               // [kUnits] (even CTA) both CTAs have drained the unit
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (2 * kTileStages + 2 + 2 * kUnits));
-    static_assert(8 * (2 * kTileStages + 2 + 2 * kUnits) + 8 <= 256, "barrier area");
+    const uint32_t bar_drain = bar_uempty + 8 * kUnits;               // 1  used only while winding down after an abort
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (2 * kTileStages + 3 + 2 * kUnits));
+    static_assert(8 * (2 * kTileStages + 3 + 2 * kUnits) + 8 <= 256, "barrier area");
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const WaitCtx wc{p.g_err, s_abort};
+    const WaitCtx wc{p.g_err, s_abort, p.wait_limit, map_to_cta(smem_u32(tmem_slot + 1), rank ^ 1)};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -618,6 +662,7 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         mbar_init(bar_res, rank == 0 ? 2 : 1);
         mbar_init(bar_resfree, 1);
+        mbar_init(bar_drain, 1);
         for (int i = 0; i < kUnits; ++i) {
             mbar_init(bar_ufull + 8 * i, 1);
             mbar_init(bar_uempty + 8 * i, 16);                 // eight drain warps of the unit's group in each CTA
@@ -663,8 +708,8 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     const uint32_t dst = s_base + C::kOffStage + s * C::kStage;
                     // box = this CTA's 64 keys of every head block -> [HP/8][64 keys][8 heads]
                     const int kb = tile * (kTileKeys / 32) + 2 * static_cast<int>(rank);
-                    tma_load_4d_hint(dst, &tm_s, 0, kb, 0, ql, bar_tfull + 8 * s, pol_stream);
-                    tma_load_4d_hint(dst + C::kHalfMat, &tm_ds, 0, kb, 0, ql, bar_tfull + 8 * s, pol_stream);
+                    tma_load_4d_hint(dst, &tm_s, 0, kb, 0, p.scr0 + ql, bar_tfull + 8 * s, pol_stream);
+                    tma_load_4d_hint(dst + C::kHalfMat, &tm_ds, 0, kb, 0, p.scr0 + ql, bar_tfull + 8 * s, pol_stream);
                     if (++s == kTileStages) {
                         s = 0;
                         ph ^= 1;
@@ -733,6 +778,10 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     }
                     umma_commit_2cta_mask(bar_resfree, 3);
                 }
+                if (*s_abort) {   // winding down: nothing of this thread's may still be in the tensor pipe at dealloc
+                    umma_commit_2cta_mask(bar_drain, 1);
+                    mbar_wait_drain(bar_drain, 0, p.wait_limit);
+                }
             }
         }
     } else {
@@ -751,14 +800,23 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         int* idx_base = reinterpret_cast<int*>(smem + C::kOffIdx) + (grp * 4 + e) * 64;
         const int bar_id = 1 + grp * 2 + e;
         const uint32_t uempty0 = map_to_cta(bar_uempty, 0);
+#ifdef SMLA_RED_EVICT_LAST
+        const uint64_t pol_keep = l2_policy_evict_last();
+#endif
         int pf[2] = {-1, -1};
+        // (the dKV row a valid slot adds to, -1 for an unused slot)
         auto fetch_idx = [&](int ql, int tile) {
+            if (ql >= nq) {
+                pf[0] = pf[1] = -1;
+                return;
+            }
+            const int qg = p.q0 + ql;
+            const QMeta qm = load_qmeta(p, qg);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int key = tile * kTileKeys + 64 * e + 32 * i + lane;
-                const int qg = p.q0 + ql;
-                const int idx = (ql < nq && key < p.topk) ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
-                pf[i] = (ql < nq && slot_valid(idx, qg, p)) ? idx : -1;
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                pf[i] = slot_valid(idx, key, qm, p) ? qm.kv_base + idx : -1;
             }
         };
         if (member == 0) fetch_idx(pair, 0);
@@ -804,8 +862,13 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
+#ifdef SMLA_RED_EVICT_LAST
+                            red_add_f32_if_row_hint(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK,
+                                                    __uint_as_float(r[j]), ix[j], pol_keep);
+#else
                             red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK,
                                                __uint_as_float(r[j]), ix[j]);
+#endif
                     }
                 }
                 // the accumulator reads have completed (tcgen05.wait::ld), which is all the issuer needs to know
@@ -815,6 +878,7 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
         }
     }
+    abort_wind_down(s_abort);
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
@@ -873,9 +937,10 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     const uint32_t bar_full = smem_u32(bars);             // [kStages]
     const uint32_t bar_empty = bar_full + 8 * kStages;    // [kStages]
     const uint32_t bar_acc = bar_empty + 8 * kStages;     // 1
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (2 * kStages + 1));
+    const uint32_t bar_drain = bar_acc + 8;               // 1  used only while winding down after an abort
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffMisc + 8 * (2 * kStages + 2));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const WaitCtx wc{p.g_err, s_abort};
+    const WaitCtx wc{p.g_err, s_abort, p.wait_limit, 0u};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -884,6 +949,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             mbar_init(bar_empty + 8 * i, 1);
         }
         mbar_init(bar_acc, 1);
+        mbar_init(bar_drain, 1);
         fence_mbar_init();
     }
     if (warp == 12) {
@@ -904,12 +970,15 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         const char* kvb = reinterpret_cast<const char*>(p.kv) + chunk0 * 128 + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
         // the indices of a tile are loaded one tile ahead, so that their latency is never in front of the copies
+        // (already translated to the kv row to read, -1: read nothing)
         int idx_next[2];
+        const QMeta qm = load_qmeta(p, qg);
         auto load_idx = [&](int tile) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int key = tile * kTileKeys + r0 + 32 * i;
-                idx_next[i] = (tile < n_tiles && key < p.topk) ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                idx_next[i] = (tile < n_tiles && key < p.topk)
+                                  ? gather_row(__ldg(p.indices + static_cast<size_t>(qg) * p.topk + key), qm, p) : -1;
             }
         };
         load_idx(0);
@@ -919,7 +988,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             uint32_t nb[2];   // 0: slot out of range, read nothing and land zeros (no shared stand-in row: it would be a hot spot)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const bool in_range = idx_next[i] >= 0 && idx_next[i] < p.s_kv;
+                const bool in_range = idx_next[i] >= 0;
                 nb[i] = in_range ? 16u : 0u;
                 src[i] = kvb + static_cast<size_t>(in_range ? idx_next[i] : 0) * (kDQK * 2);
             }
@@ -942,7 +1011,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
                 const uint32_t dst = s_base + s * C::kStage;
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes);
                 // box = 64 keys of every head block -> [HP/8][64 keys][8 heads]
-                tma_load_4d_hint(dst + C::kKgBytes, &tm_ds, 0, tile * (kTileKeys / 32), 0, ql, bar_full + 8 * s, pol_stream);
+                tma_load_4d_hint(dst + C::kKgBytes, &tm_ds, 0, tile * (kTileKeys / 32), 0, p.scr0 + ql, bar_full + 8 * s, pol_stream);
             }
         }
     } else if (warp == 12) {
@@ -970,6 +1039,10 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
                 umma_commit(bar_empty + 8 * s);
             }
             umma_commit(bar_acc);
+            if (*s_abort) {   // winding down: nothing of this thread's may still be in the tensor pipe at dealloc
+                umma_commit(bar_drain);
+                mbar_wait_drain(bar_drain, 0, p.wait_limit);
+            }
         }
     } else {
         const int quarter = warp;
@@ -1006,9 +1079,43 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             }
         }
     }
+    abort_wind_down(s_abort);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 12) tmem_dealloc(tmem, C::kTmemCols);
+}
+
+// =============================================================================================
+// Self-test of the bounded waits: one CTA waits on a barrier (or a counter) that nothing ever signals, with a
+// short limit.  The wait must give up, record `code`, raise the abort flag, and the kernel must return
+// normally; a second wait must then return at once.  out[0] = what the first wait returned, out[1] = what
+// the second returned, out[2] = cycles the first wait took.
+// =============================================================================================
+__global__ void __launch_bounds__(32) smla_selftest_wait_kernel(int* g_err, long long* out, int which, long long limit,
+                                                                int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    __shared__ uint32_t counter;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        counter = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const WaitCtx wc{g_err, &abort_flag, limit, 0u};
+        const long long t0 = clock64();
+        bool a;
+        if (which == 0) a = mbar_wait(smem_u32(&bar), 0, wc, code, kPollSleepNs);
+        else if (which == 1) a = mbar_spin(smem_u32(&bar), 0, wc, code);
+        else a = flag_wait(smem_u32(&counter), 1u, wc, code);
+        const long long t1 = clock64();
+        const bool b = mbar_wait(smem_u32(&bar), 0, wc, code + 1);
+        out[0] = a ? 1 : 0;
+        out[1] = b ? 1 : 0;
+        out[2] = t1 - t0;
+    }
 }
 
 }  // namespace smla

@@ -33,6 +33,7 @@ class _Params(ctypes.Structure):
         ("O", ctypes.c_void_p), ("indices", ctypes.c_void_p), ("dQ", ctypes.c_void_p), ("dKV", ctypes.c_void_p),
         ("s_q", ctypes.c_int32), ("s_kv", ctypes.c_int32), ("h_q", ctypes.c_int32), ("topk", ctypes.c_int32),
         ("sm_scale", ctypes.c_float), ("q_start_index_s", ctypes.c_int32), ("lse_is_base2", ctypes.c_int32),
+        ("query_meta", ctypes.c_void_p),
     ]
 
 
@@ -42,6 +43,7 @@ class _FwdParams(ctypes.Structure):
         ("lse", ctypes.c_void_p),
         ("s_q", ctypes.c_int32), ("s_kv", ctypes.c_int32), ("h_q", ctypes.c_int32), ("topk", ctypes.c_int32),
         ("sm_scale", ctypes.c_float), ("q_start_index_s", ctypes.c_int32), ("lse_is_base2", ctypes.c_int32),
+        ("query_meta", ctypes.c_void_p),
     ]
 
 
@@ -116,6 +118,18 @@ def load_library() -> ctypes.CDLL:
         lib.smla_index_inverse.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                            ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                            ctypes.c_size_t, ctypes.c_void_p]
+        lib.smla_bwd_workspace_init.restype = ctypes.c_int
+        lib.smla_bwd_workspace_init.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.smla_bwd_last_device_code.restype = ctypes.c_int
+        lib.smla_bwd_set_schedule.restype = ctypes.c_int
+        lib.smla_bwd_set_schedule.argtypes = [ctypes.c_int, ctypes.c_int]
+        lib.smla_bwd_get_schedule.restype = None
+        lib.smla_bwd_get_schedule.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        lib.smla_debug_set_wait_limit_cycles.restype = ctypes.c_int
+        lib.smla_debug_set_wait_limit_cycles.argtypes = [ctypes.c_longlong]
+        lib.smla_selftest_wait_timeout.restype = ctypes.c_int
+        lib.smla_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p,
+                                                   ctypes.c_void_p]
         lib.smla_bwd_status_string = lib.smla_status_string
         lib.smla_status_string.restype = ctypes.c_char_p
         lib.smla_status_string.argtypes = [ctypes.c_int]
@@ -134,10 +148,14 @@ def _raise_status(lib, status: int, what: str) -> None:
 
 
 class Workspace:
-    """Device scratch owned by the caller (delta, bf16 S / dS, error word); reusable across calls."""
+    """Device scratch owned by the caller (delta, bf16 S / dS, error word); reusable across calls.
+
+    The first 256 bytes hold the device error word and start at zero; the kernels only ever set it, and
+    `device_status` clears it after reporting."""
 
     def __init__(self, nbytes: int, device):
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf[:256].zero_()
         self.nbytes = nbytes
 
     @property
@@ -145,7 +163,33 @@ class Workspace:
         return self.buf.data_ptr()
 
 
-def _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV2, sm_scale, q_start_index_s, lse_is_base2) -> _Params:
+# Workspaces handed out when the caller passes none, one per (device, stream) so that calls queued on different
+# streams do not share scratch; kept (and grown when a larger problem comes) instead of allocating gigabytes per call.
+_ws_cache = {}
+_ws_cache_lock = threading.Lock()
+
+
+def _cached_workspace(need: int, device: torch.device) -> Workspace:
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    with _ws_cache_lock:
+        ws = _ws_cache.get(key)
+        if ws is None or ws.nbytes < need:
+            _ws_cache.pop(key, None)
+            ws = None                       # let the smaller one go before the larger one is allocated
+            ws = Workspace(need, device)
+            _ws_cache[key] = ws
+        return ws
+
+
+def release_cached_workspaces() -> None:
+    """Drop the workspaces kept for calls that pass none (they are re-created on demand)."""
+    with _ws_cache_lock:
+        _ws_cache.clear()
+
+
+def _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV2, sm_scale, q_start_index_s, lse_is_base2,
+                 query_meta=None) -> _Params:
     return _Params(
         q.data_ptr(), kv2.data_ptr(), dO.data_ptr(), lse.data_ptr(), O.data_ptr(), idx2.data_ptr(),
         dQ.data_ptr(), dKV2.data_ptr(),
@@ -153,7 +197,22 @@ def _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV2, sm_scale, q_start_index_s, 
         float(sm_scale) if sm_scale is not None else 0.0,
         NO_CAUSAL if q_start_index_s is None else int(q_start_index_s),
         1 if lse_is_base2 else 0,
+        query_meta.data_ptr() if query_meta is not None else None,
     )
+
+
+def _check_query_meta(query_meta, q) -> None:
+    if query_meta is None:
+        return
+    _check(isinstance(query_meta, torch.Tensor) and query_meta.is_cuda and query_meta.device == q.device
+           and query_meta.dtype == torch.int32 and query_meta.is_contiguous()
+           and tuple(query_meta.shape) == (q.shape[0], 4) and query_meta.data_ptr() % 16 == 0,
+           "query_meta must be a contiguous int32 CUDA tensor [s_q, 4] on q's device")
+
+
+def _check_out(t, like_shape_numel, dtype, device, name) -> None:
+    _check(isinstance(t, torch.Tensor) and t.is_cuda and t.device == device and t.dtype == dtype and t.is_contiguous()
+           and t.numel() == like_shape_numel, f"{name} must be a contiguous {dtype} CUDA tensor of {like_shape_numel} elements on {device}")
 
 
 def _validate(q, kv, dO, lse, O, indices):
@@ -198,34 +257,44 @@ def mla_bwd(
     workspace: Optional[Workspace] = None,
     workspace_budget: int = 0,
     check_device_status: bool = False,
+    out_dq: Optional[torch.Tensor] = None,
+    query_meta: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sparse MLA attention backward.  Returns (dQ bf16 [s_q,h_q,576], dKV fp32 shaped like kv).
 
     Positional arguments and defaults are the reference operator's: base-2 `lse`, sm_scale =
     1/sqrt(576), and the causal rule "slot valid only if idx <= query row" (`q_start_index_s=0`,
     `mla_bwd/mla_bwd.cu:122,772`).  Pass `q_start_index_s=None` to keep only the range check.
-    `out_dkv` + `accumulate=True` add into an existing fp32 buffer (partial dKV of a query shard).
-    The call enqueues on the current stream and does not synchronise unless
+    `out_dkv` + `accumulate=True` add into an existing fp32 buffer (partial dKV of a query shard);
+    `out_dq` receives dQ in place.  `query_meta` (int32 [s_q, 4] on the device: first kv row and number of
+    kv rows of the query's sequence, position for the causal rule, top-k slots in use) lets one call cover
+    packed sequences; see `query_meta_for`.  Without `workspace` the scratch comes from a cache kept per
+    (device, stream).  The call enqueues on the current stream and does not synchronise unless
     `check_device_status=True`, which also raises if a kernel reported a timed-out wait.
     """
     _validate(q, kv, dO, lse, O, indices)
+    _check_query_meta(query_meta, q)
     lib = load_library()
     kv2 = kv.reshape(kv.shape[0], D_QK)
     idx2 = indices.reshape(indices.shape[0], indices.shape[-1])
     with torch.cuda.device(q.device):
-        dQ = torch.empty_like(q)
+        if out_dq is None:
+            dQ = torch.empty_like(q)
+        else:
+            _check_out(out_dq, q.numel(), torch.bfloat16, q.device, "out_dq")
+            dQ = out_dq
         if out_dkv is None:
             dKV = torch.empty(kv.shape, dtype=torch.float32, device=q.device)
             _check(not accumulate, "accumulate=True needs out_dkv")
         else:
-            _check(out_dkv.is_cuda and out_dkv.dtype == torch.float32 and out_dkv.is_contiguous()
-                   and out_dkv.numel() == kv.numel(), "out_dkv must be a contiguous fp32 CUDA tensor shaped like kv")
+            _check_out(out_dkv, kv.numel(), torch.float32, q.device, "out_dkv")
             dKV = out_dkv
-        params = _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV, sm_scale, q_start_index_s, lse_is_base2)
+        params = _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV, sm_scale, q_start_index_s, lse_is_base2, query_meta)
         if workspace is None:
             need = lib.smla_bwd_workspace_size(ctypes.byref(params), workspace_budget)
             _check(need > 0, "unsupported shapes for the sparse MLA backward")
-            workspace = Workspace(need, q.device)
+            # a budget asks for a particular size: do not serve it from a (possibly larger) cached one
+            workspace = Workspace(need, q.device) if workspace_budget else _cached_workspace(need, q.device)
         stream = torch.cuda.current_stream().cuda_stream
         stages = STAGE_ALL & ~STAGE_ZERO if accumulate else STAGE_ALL
         st = lib.smla_bwd_run_stages(ctypes.byref(params), workspace.ptr, workspace.nbytes, stream, stages)
@@ -235,78 +304,86 @@ def mla_bwd(
     return dQ, dKV
 
 
-def _apply_topk_length(indices: torch.Tensor, topk_length: Optional[torch.Tensor]) -> torch.Tensor:
-    """Slots at or beyond a query's `topk_length` become unused (-1)."""
-    if topk_length is None:
-        return indices
-    _check(topk_length.shape == indices.shape[:-1] and not topk_length.is_floating_point(),
-           "topk_length must be an integer tensor shaped like indices without its last dimension")
-    slot = torch.arange(indices.shape[-1], device=indices.device)
-    return torch.where(slot < topk_length.unsqueeze(-1).to(indices.device), indices, indices.new_full((), -1)).contiguous()
+def query_meta_for(seq_q_start, seq_q_len, seq_kv_start, seq_kv_len, device, q_start_index_s: Optional[int] = 0,
+                   topk: int = 0, topk_length: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-query table for packed sequences: int32 [T_q, 4] = (first kv row of the query's sequence, kv rows of
+    that sequence, position for the causal rule = q_start_index_s + row inside the sequence, top-k slots in use).
+
+    `seq_*` are host integer sequences (one entry per sequence, queries and kv rows packed in that order);
+    `topk_length` ([T_q], optional) limits the slots in use per query, the per-query field of the reference's
+    richer parameter block (`dq_test/dq_phase_capture.cuh:107-109`)."""
+    n_seq = len(seq_q_len)
+    lens = torch.tensor(list(seq_q_len), dtype=torch.int64)
+    seq_of_q = torch.repeat_interleave(torch.arange(n_seq), lens)
+    t_q = int(lens.sum().item())
+    row_in_seq = torch.arange(t_q) - torch.tensor(list(seq_q_start), dtype=torch.int64)[seq_of_q]
+    meta = torch.empty(t_q, 4, dtype=torch.int32)
+    meta[:, 0] = torch.tensor(list(seq_kv_start), dtype=torch.int32)[seq_of_q]
+    meta[:, 1] = torch.tensor(list(seq_kv_len), dtype=torch.int32)[seq_of_q]
+    meta[:, 2] = (row_in_seq + (q_start_index_s or 0)).to(torch.int32)
+    meta[:, 3] = topk
+    meta = meta.to(device)
+    if topk_length is not None:
+        _check(not topk_length.is_floating_point() and topk_length.numel() == t_q, "topk_length must be an integer tensor with one entry per query")
+        meta[:, 3] = topk_length.reshape(-1).to(device=device, dtype=torch.int32).clamp(0, topk)
+    return meta.contiguous()
 
 
-def mla_bwd_batched(q, kv, dO, lse, O, indices, topk_length: Optional[torch.Tensor] = None, **kwargs):
+def mla_bwd_batched(q, kv, dO, lse, O, indices, topk_length: Optional[torch.Tensor] = None,
+                    q_start_index_s: Optional[int] = 0, **kwargs):
     """Backward for a batch of independent sequences of equal shape, so that callers stop looping themselves.
 
     q / dO / O [B, s_q, h_q, d], kv [B, s_kv, 576] (or [B, s_kv, 1, 576]), lse [B, s_q, h_q], indices [B, s_q, topk]
-    with values relative to the own sequence's kv; `topk_length` [B, s_q] (optional) limits the slots in use per query,
-    the per-query field of the reference's richer parameter block (`dq_test/dq_phase_capture.cuh:107-109`).  One
-    workspace serves all sequences; the kernels of consecutive sequences queue on the current stream.  Returns
-    (dQ [B, s_q, h_q, 576] bf16, dKV fp32 shaped like kv).  Keyword arguments as for `mla_bwd` (without out_dkv).
+    with values relative to the own sequence's kv; `topk_length` [B, s_q] (optional) limits the slots in use per query.
+    The batch runs as ONE chain of kernels over all B * s_q queries (a per-query table tells the kernels which kv rows
+    a query may touch), writing dQ and dKV in place.  Returns (dQ [B, s_q, h_q, 576] bf16, dKV fp32 shaped like kv).
+    Keyword arguments as for `mla_bwd` (without out_dkv / out_dq).
     """
     _check(q.dim() == 4 and kv.dim() in (3, 4) and indices.dim() == 3, "batched tensors need a leading batch dimension")
-    B = q.shape[0]
+    B, s_q = q.shape[0], q.shape[1]
+    s_kv = kv.shape[1]
     _check(all(t.shape[0] == B for t in (kv, dO, lse, O, indices)), "batch sizes differ")
-    _check("out_dkv" not in kwargs and "accumulate" not in kwargs, "mla_bwd_batched allocates its outputs")
-    idx = _apply_topk_length(indices, topk_length)
-    ws = kwargs.pop("workspace", None) or workspace_for(q[0], kv[0], idx[0], kwargs.pop("workspace_budget", 0))
+    for k in ("out_dkv", "accumulate", "out_dq", "query_meta"):
+        _check(k not in kwargs, "mla_bwd_batched allocates its outputs and builds its own query table")
+    meta = query_meta_for([b * s_q for b in range(B)], [s_q] * B, [b * s_kv for b in range(B)], [s_kv] * B, q.device,
+                          q_start_index_s, indices.shape[-1], topk_length)
     dQ = torch.empty_like(q)
     dKV = torch.empty(kv.shape, dtype=torch.float32, device=q.device)
-    for b in range(B):
-        dq_b, _ = mla_bwd(q[b], kv[b], dO[b], lse[b], O[b], idx[b], out_dkv=dKV[b], workspace=ws, **kwargs)
-        dQ[b].copy_(dq_b)
+    mla_bwd(q.reshape(B * s_q, *q.shape[2:]), kv.reshape(B * s_kv, D_QK), dO.reshape(B * s_q, *dO.shape[2:]),
+            lse.reshape(B * s_q, -1), O.reshape(B * s_q, *O.shape[2:]), indices.reshape(B * s_q, -1),
+            q_start_index_s=q_start_index_s, out_dq=dQ, out_dkv=dKV, query_meta=meta, **kwargs)
     return dQ, dKV
 
 
 def mla_bwd_varlen(q, kv, dO, lse, O, indices, cu_seqlens_q, cu_seqlens_kv, topk_length: Optional[torch.Tensor] = None,
-                   **kwargs):
+                   q_start_index_s: Optional[int] = 0, **kwargs):
     """Backward for sequences of different lengths packed along the first dimension.
 
     q / dO / O [T_q, h_q, d], lse [T_q, h_q], indices [T_q, topk], kv [T_kv, 576]; sequence i owns query rows
     cu_seqlens_q[i]:cu_seqlens_q[i+1] and kv rows cu_seqlens_kv[i]:cu_seqlens_kv[i+1] (host integer sequences or CPU
     tensors, as in the usual varlen attention interfaces).  Index values are relative to the own sequence's first kv
-    row; `q_start_index_s` applies to every sequence from its own first query.  Returns (dQ [T_q, h_q, 576] bf16,
-    dKV [T_kv, 576] fp32).  Empty sequences are allowed.
+    row; `q_start_index_s` applies to every sequence from its own first query.  All sequences run as ONE chain of
+    kernels.  Returns (dQ [T_q, h_q, 576] bf16, dKV [T_kv, 576] fp32).  Empty sequences are allowed.
     """
     cq = [int(v) for v in cu_seqlens_q]
     ck = [int(v) for v in cu_seqlens_kv]
     _check(len(cq) == len(ck) and len(cq) >= 2 and cq[0] == 0 and ck[0] == 0, "cu_seqlens must start at 0 and match in length")
     _check(cq[-1] == q.shape[0] and ck[-1] == kv.shape[0], "cu_seqlens do not cover q / kv")
     _check(all(a <= b for a, b in zip(cq, cq[1:])) and all(a <= b for a, b in zip(ck, ck[1:])), "cu_seqlens must not decrease")
-    _check("out_dkv" not in kwargs and "accumulate" not in kwargs, "mla_bwd_varlen allocates its outputs")
-    idx = _apply_topk_length(indices, topk_length)
-    budget = kwargs.pop("workspace_budget", 0)
-    ws = kwargs.pop("workspace", None)
-    dQ = torch.empty_like(q)
-    dKV = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)      # sequences without queries keep zeros
-    longest = max(range(len(cq) - 1), key=lambda i: cq[i + 1] - cq[i])
-    for i in range(len(cq) - 1):
-        q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i + 1]
-        if q1 == q0 or k1 == k0:
-            _check(q1 == q0, "a sequence with queries needs kv rows")
-            continue
-        if ws is None:       # sized for the longest sequence; shorter ones take fewer passes through it
-            l0, l1 = cq[longest], cq[longest + 1]
-            ws = workspace_for(q[l0:l1], kv[k0:k1], idx[l0:l1], budget)
-        dq_i, _ = mla_bwd(q[q0:q1], kv[k0:k1], dO[q0:q1], lse[q0:q1], O[q0:q1], idx[q0:q1], out_dkv=dKV[k0:k1],
-                          workspace=ws, **kwargs)
-        dQ[q0:q1].copy_(dq_i)
-    return dQ, dKV
+    _check(all(q1 == q0 or k1 > k0 for q0, q1, k0, k1 in zip(cq, cq[1:], ck, ck[1:])), "a sequence with queries needs kv rows")
+    for k in ("out_dkv", "accumulate", "out_dq", "query_meta"):
+        _check(k not in kwargs, "mla_bwd_varlen allocates its outputs and builds its own query table")
+    if q.shape[0] == 0:
+        return torch.empty_like(q), torch.zeros(kv.shape, dtype=torch.float32, device=q.device)
+    meta = query_meta_for(cq[:-1], [b - a for a, b in zip(cq, cq[1:])], ck[:-1], [b - a for a, b in zip(ck, ck[1:])],
+                          q.device, q_start_index_s, indices.shape[-1], topk_length)
+    return mla_bwd(q, kv, dO, lse, O, indices, q_start_index_s=q_start_index_s, query_meta=meta, **kwargs)
 
 
 def mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: Optional[float] = None,
             q_start_index_s: Optional[int] = 0, lse_is_base2: bool = True, workspace: Optional[Workspace] = None,
-            workspace_budget: int = 0, check_device_status: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+            workspace_budget: int = 0, check_device_status: bool = False,
+            query_meta: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sparse MLA attention forward for the same top-k indices: returns (o bf16 [s_q,h_q,512], lse fp32 [s_q,h_q]).
 
     The reference has no forward operator; its tests make o / lse with fp32 torch code
@@ -322,6 +399,7 @@ def mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: 
            "indices must be [s_q,topk] or [s_q,1,topk]")
     s_q, h_q, _ = q.shape
     _check(0 < h_q <= 128 and h_q % 8 == 0, f"h_q must be a multiple of 8 in [8, 128], got {h_q}")
+    _check_query_meta(query_meta, q)
     lib = load_library()
     with torch.cuda.device(q.device):
         o = torch.empty(s_q, h_q, D_V, dtype=torch.bfloat16, device=q.device)
@@ -329,7 +407,8 @@ def mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: 
         params = _FwdParams(q.data_ptr(), kv.data_ptr(), indices.data_ptr(), o.data_ptr(), lse.data_ptr(),
                             s_q, kv.shape[0], h_q, indices.shape[-1],
                             float(sm_scale) if sm_scale is not None else 0.0,
-                            NO_CAUSAL if q_start_index_s is None else int(q_start_index_s), 1 if lse_is_base2 else 0)
+                            NO_CAUSAL if q_start_index_s is None else int(q_start_index_s), 1 if lse_is_base2 else 0,
+                            query_meta.data_ptr() if query_meta is not None else None)
         if workspace is None:
             need = lib.smla_fwd_workspace_size(ctypes.byref(params), workspace_budget)
             _check(need > 0, "unsupported shapes for the sparse MLA forward")
@@ -395,6 +474,8 @@ def mla_bwd_noalloc(q, kv, dO, lse, O, indices, dQ, dKV, sm_scale: Optional[floa
     `smla_bwd_run_noalloc` in include/smla_bwd.h for who they are and for the size limit).  Calls on one device
     must not overlap: they share the scratch."""
     _validate(q, kv, dO, lse, O, indices)
+    _check_out(dQ, q.numel(), torch.bfloat16, q.device, "dQ")
+    _check_out(dKV, kv.numel(), torch.float32, q.device, "dKV")
     lib = load_library()
     params = _make_params(q, kv.view(kv.shape[0], D_QK), dO, lse, O, indices.view(indices.shape[0], indices.shape[-1]),
                           dQ, dKV, sm_scale, q_start_index_s, lse_is_base2)
@@ -425,16 +506,34 @@ def run_stages(q, kv, dO, lse, O, indices, dQ, dKV, workspace: Workspace, stages
 def workspace_for(q, kv, indices, budget: int = 0) -> Workspace:
     """Allocate a workspace big enough for these shapes (at most about `budget` bytes when non-zero)."""
     lib = load_library()
-    p = _Params(0, 0, 0, 0, 0, 0, 0, 0, q.shape[0], kv.shape[0], q.shape[1], indices.shape[-1], 0.0, 0, 1)
+    p = _Params(0, 0, 0, 0, 0, 0, 0, 0, q.shape[0], kv.shape[0], q.shape[1], indices.shape[-1], 0.0, 0, 1, None)
     need = lib.smla_bwd_workspace_size(ctypes.byref(p), budget)
     _check(need > 0, "unsupported shapes for the sparse MLA backward")
     return Workspace(need, q.device)
 
 
 def device_status(workspace: Workspace) -> int:
-    """Synchronise the current stream and return the library status word (0 = ok)."""
+    """Synchronise the current stream and return the library status (0 = ok, 4 = a bounded wait inside a kernel of
+    any call since the last check ran out).  A recorded timeout is reported once and cleared."""
     lib = load_library()
     return lib.smla_bwd_status(workspace.ptr, torch.cuda.current_stream().cuda_stream)
+
+
+def last_device_code() -> int:
+    """Raw error word the last `device_status` on this thread read: 0, or 100 * kernel + site of the wait that gave up."""
+    return load_library().smla_bwd_last_device_code()
+
+
+def set_schedule(chunks: int, dkv_pairs: int) -> None:
+    """How one pass of the backward is scheduled (`smla_bwd_set_schedule`): 0 chunks = one kernel after the other."""
+    lib = load_library()
+    _raise_status(lib, lib.smla_bwd_set_schedule(int(chunks), int(dkv_pairs)), "smla_bwd_set_schedule")
+
+
+def get_schedule() -> Tuple[int, int]:
+    c, d = ctypes.c_int(0), ctypes.c_int(0)
+    load_library().smla_bwd_get_schedule(ctypes.byref(c), ctypes.byref(d))
+    return c.value, d.value
 
 
 def delta(O: torch.Tensor, dO: torch.Tensor) -> torch.Tensor:

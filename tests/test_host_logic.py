@@ -25,6 +25,16 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, n), f"{n} declared in include/smla_bwd.h but not exported"
 
 
+def test_extension_module_is_compiled_code_and_checks_like_the_reference():
+    """`python setup.py build_ext --inplace` (run by `__graft_entry__.build()`) leaves the module `mla_bwd_cuda` in the
+    tree: a compiled extension exporting `mla_bwd`, as `mla_bwd/setup.py:61-78` / `mla_bwd/mla_bwd.cu:1060-1063` do."""
+    mod = pytest.importorskip("mla_bwd_cuda")
+    assert mod.__file__.endswith(".so") and callable(mod.mla_bwd)
+    t = torch.zeros(2, 16, 576, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):       # TORCH_CHECK -> RuntimeError (mla_bwd.cu:975-1015)
+        mod.mla_bwd(t, t, t, t, t, t)
+
+
 def test_struct_layout_matches_header_field_order():
     hdr = open(os.path.join(ROOT, "include", "smla_bwd.h")).read()
     body = hdr[hdr.index("typedef struct smla_bwd_params {"): hdr.index("} smla_bwd_params;")]

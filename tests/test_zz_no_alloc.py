@@ -40,12 +40,39 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
         dq = torch.full_like(t["q"], float("nan"))
         dkv = torch.full(t["kv"].shape, float("nan"), dtype=torch.float32, device=DEV)
         p = _params(op, t, dq, dkv, None)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        torch_before = torch.cuda.memory_allocated()
         st = lib.smla_bwd_run_noalloc(ctypes.byref(p), stream)
         assert st == 0, lib.smla_status_string(st)
         assert lib.smla_bwd_noalloc_status(stream) == 0
+        if call == 1:
+            # what the entry point is for: the device's free memory and torch's books are where they were (the first
+            # call may still have made the driver load the kernels' code, so the second one is the one held to it)
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.memory_allocated() == torch_before
         assert lib.smla_bwd_last_launch_count() >= 1 + 3 * 3      # Delta + three kernels per pass, three passes
         assert torch.equal(dq.view(torch.int16), dq_ref.view(torch.int16)), f"dQ differs on call {call}"
         assert (dkv - dkv_ref).abs().max().item() <= 1e-5 * dkv_ref.abs().max().item(), f"dKV differs on call {call}"
+
+
+def test_noalloc_python_wrapper_validates_and_matches():
+    from test_operator_b200 import op
+    w = Workload("noalloc_py", 1, 40, 1024, 64, 256, "uniform", invalid_frac=0.1)
+    seq = make_sequence(w, device=DEV, seed=32)
+    t = {k: v for k, v in seq.items() if torch.is_tensor(v)}
+    dq_ref, dkv_ref = op.mla_bwd(t["q"], t["kv"], t["dO"], t["lse"], t["O"], t["indices"], q_start_index_s=None,
+                                 check_device_status=True)
+    dq = torch.empty_like(t["q"])
+    dkv = torch.empty(t["kv"].shape, dtype=torch.float32, device=DEV)
+    op.mla_bwd_noalloc(t["q"], t["kv"], t["dO"], t["lse"], t["O"], t["indices"], dq, dkv, q_start_index_s=None)
+    assert op.load_library().smla_bwd_noalloc_status(torch.cuda.current_stream().cuda_stream) == 0
+    assert torch.equal(dq.view(torch.int16), dq_ref.view(torch.int16))
+    assert (dkv - dkv_ref).abs().max().item() <= 1e-5 * dkv_ref.abs().max().item()
+    with pytest.raises(RuntimeError):      # outputs of the wrong size or type never reach the kernels
+        op.mla_bwd_noalloc(t["q"], t["kv"], t["dO"], t["lse"], t["O"], t["indices"], dq[:-1], dkv, q_start_index_s=None)
+    with pytest.raises(RuntimeError):
+        op.mla_bwd_noalloc(t["q"], t["kv"], t["dO"], t["lse"], t["O"], t["indices"], dq, dkv.double(), q_start_index_s=None)
 
 
 def test_noalloc_entry_refuses_what_cannot_fit():
