@@ -181,6 +181,11 @@ void smla_bwd_get_schedule(int* chunks, int* dkv_pairs);
 int smla_debug_set_wait_limit_cycles(long long cycles);
 int smla_selftest_wait_timeout(void* workspace, int which, long long limit_cycles, long long* out3, void* stream);
 
+/* Measurement aid: every SM that gets a block writes {its cycle counter, the global nanosecond timer} to
+ * out[2 * smid], out[2 * smid + 1] (device memory, 2 * n_sm x u64; SMs that got none keep what was there).  Two probes
+ * around a timed region give the average SM clock inside it: delta cycles / delta ns per SM. */
+int smla_clock_probe(unsigned long long* out, int n_sm, void* stream);
+
 /* Number of kernels (own kernels, memset excluded) the last smla_bwd_run_stages on this thread launched. */
 int smla_bwd_last_launch_count(void);
 

@@ -704,6 +704,26 @@ int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
 }
 
+// ---- SM clock probe ------------------------------------------------------------------------------------------
+namespace {
+__global__ void clock_probe_kernel(unsigned long long* out, int n_sm) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (static_cast<int>(smid) < n_sm) {
+        out[2 * smid] = static_cast<unsigned long long>(clock64());
+        out[2 * smid + 1] = t;
+    }
+}
+}  // namespace
+
+int smla_clock_probe(unsigned long long* out, int n_sm, void* stream) {
+    if (!out || n_sm <= 0) return SMLA_ERR_BAD_ARG;
+    clock_probe_kernel<<<4 * n_sm, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(out, n_sm);
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
+
 int smla_bwd_last_launch_count(void) { return g_last_launches; }
 
 const char* smla_status_string(int status) {

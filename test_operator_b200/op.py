@@ -130,6 +130,8 @@ def load_library() -> ctypes.CDLL:
         lib.smla_selftest_wait_timeout.restype = ctypes.c_int
         lib.smla_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p,
                                                    ctypes.c_void_p]
+        lib.smla_clock_probe.restype = ctypes.c_int
+        lib.smla_clock_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.smla_bwd_status_string = lib.smla_status_string
         lib.smla_status_string.restype = ctypes.c_char_p
         lib.smla_status_string.argtypes = [ctypes.c_int]
@@ -547,6 +549,36 @@ def delta(O: torch.Tensor, dO: torch.Tensor) -> torch.Tensor:
                                 torch.cuda.current_stream().cuda_stream)
     _raise_status(lib, st, "smla_bwd_delta")
     return out
+
+
+class SMClock:
+    """Average SM clock between two points of the current stream, from the SMs' own cycle counters."""
+
+    def __init__(self, device):
+        self.lib = load_library()
+        self.n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+        self.a = torch.zeros(self.n_sm, 2, dtype=torch.int64, device=device)
+        self.b = torch.zeros(self.n_sm, 2, dtype=torch.int64, device=device)
+
+    def _probe(self, buf):
+        buf.zero_()
+        _raise_status(self.lib, self.lib.smla_clock_probe(buf.data_ptr(), self.n_sm, torch.cuda.current_stream().cuda_stream),
+                      "smla_clock_probe")
+
+    def begin(self):
+        self._probe(self.a)
+
+    def end(self):
+        self._probe(self.b)
+
+    def mhz(self) -> Optional[float]:
+        """Call after a synchronise.  Mean over the SMs both probes reached of delta cycles / delta microseconds."""
+        a, b = self.a.cpu(), self.b.cpu()
+        ok = (a[:, 1] > 0) & (b[:, 1] > a[:, 1])
+        if not ok.any():
+            return None
+        d = (b[ok] - a[ok]).double()
+        return float((d[:, 0] / d[:, 1] * 1e3).mean().item())
 
 
 def last_launch_count() -> int:
