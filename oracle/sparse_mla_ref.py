@@ -8,8 +8,11 @@ and only as the checker or as the timed CPU baseline.
 
 Parity pinning: the reference stores no golden vectors for this path (every test
 regenerates seeded random inputs).  The restatement is therefore pinned against outputs
-of the reference function itself, executed on CPU tensors by
-`tests/golden/make_golden.py`; the resulting vectors live in `tests/golden/*.npz`.
+of the reference functions themselves, executed on CPU tensors: the backward by
+`tests/golden/make_golden.py` (`build_reference` of `mla_bwd/test_mla_bwd.py`, bit-identical),
+the forward and the natural-log-lse / query-start semantics by
+`tests/golden/make_golden_fwd.py` (`build_reference` of `dq_test/test_dq_phase.py`);
+the resulting vectors live in `tests/golden/*.npz`.
 
 The functions are plain torch and run on whatever device their inputs live on: on CPU tensors they
 are the CPU oracle (and the timed CPU baseline); on CUDA tensors the same fp32 arithmetic runs in

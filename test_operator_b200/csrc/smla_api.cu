@@ -38,8 +38,8 @@ thread_local int g_last_device_code = 0;
 constexpr int kMaxChunks = 16;
 std::atomic<int> g_sched_chunks{-1};      // -1: not yet read from the environment
 std::atomic<int> g_sched_dkv_pairs{0};
-constexpr int kDefaultChunks = 0;
-constexpr int kDefaultDkvPairs = 0;
+constexpr int kDefaultChunks = 2;         // measured on B200: two parts beat three and more (each launch has its own tail)
+constexpr int kDefaultDkvPairs = 0;       // 0: chosen from the head count, see auto_dkv_pairs
 std::atomic<long long> g_wait_limit{smla::kWaitLimitCycles};
 
 void schedule(int* chunks, int* dkv_pairs) {
@@ -59,6 +59,17 @@ void schedule(int* chunks, int* dkv_pairs) {
     }
     *chunks = c;
     *dkv_pairs = g_sched_dkv_pairs.load();
+}
+
+// Clusters for the dkv kernel when the caller leaves the choice to the library: its share of the three kernels'
+// time, measured with each kernel alone on a whole B200 (top-k 2048; dkv 3.8 ms at either head count, recompute +
+// dq 3.4 ms at 128 heads and 2.65 ms at 64).  The step time is flat within +-3 clusters of these.
+int auto_dkv_pairs(int h_pad, int resident) {
+    const double share = h_pad > 64 ? 0.50 : 0.58;
+    int n = static_cast<int>(resident * share + 0.5);
+    if (n < 1) n = 1;
+    if (n > resident - 1) n = resident - 1;
+    return n;
 }
 
 // Second stream and the events that order it against the caller's stream, one set per device, created on the first
@@ -307,7 +318,8 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     int chunks = 0, dkv_pairs = 0;
     schedule(&chunks, &dkv_pairs);
     const int all = SMLA_STAGE_RECOMPUTE | SMLA_STAGE_DKV | SMLA_STAGE_DQ;
-    if (!allow_overlap || (stages & all) != all || dkv_pairs <= 0 || dkv_pairs >= pairs_d || dkv_pairs >= pairs_r) chunks = 0;
+    if (dkv_pairs <= 0) dkv_pairs = auto_dkv_pairs(HP, pairs_d < pairs_r ? pairs_d : pairs_r);
+    if (!allow_overlap || (stages & all) != all || dkv_pairs >= pairs_d || dkv_pairs >= pairs_r) chunks = 0;
 
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
@@ -532,7 +544,7 @@ int smla_bwd_workspace_init(void* workspace, void* stream) {
 }
 
 int smla_bwd_set_schedule(int chunks, int dkv_pairs) {
-    if (chunks < 0 || chunks > kMaxChunks || chunks == 1 || dkv_pairs < 0) return SMLA_ERR_BAD_ARG;
+    if (chunks < 0 || chunks > kMaxChunks || chunks == 1 || dkv_pairs < 0) return SMLA_ERR_BAD_ARG;   // dkv_pairs 0: automatic
     g_sched_dkv_pairs.store(dkv_pairs);
     g_sched_chunks.store(chunks);
     return SMLA_OK;

@@ -254,18 +254,19 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         const uint64_t pol_keep = l2_policy_evict_last();
         // index of slot (tile, row i) of query ql, -1 past the top-k; the loads for the next tile are issued
         // before the current tile's copies so that their latency never stalls the ring
-        // (already translated to the kv row to read, -1: read nothing)
+        // (raw values: nothing may depend on a load here, or the wait for it would sit in front of the copies; they are
+        // turned into kv rows one tile later, when they are used)
+        QMeta qm_next = load_qmeta(p, p.q0 + (pair < nq ? pair : 0));
         auto load_idx = [&](int ql, int tile, int (&idx)[4]) {
             if (ql >= nq) {
                 idx[0] = idx[1] = idx[2] = idx[3] = -1;
                 return;
             }
-            const QMeta qm = load_qmeta(p, p.q0 + ql);
+            if (tile == 0) qm_next = load_qmeta(p, p.q0 + ql);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = tile * kTileKeys + rank * 128 + r0 + 32 * i;
-                idx[i] = key < p.topk
-                             ? gather_row(__ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key), qm, p) : -1;
+                idx[i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
             }
         };
         int idx_next[4];
@@ -281,9 +282,9 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 uint32_t nb[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const bool in_range = idx_next[i] >= 0;
-                    nb[i] = in_range ? 16u : 0u;
-                    src[i] = kvb + static_cast<size_t>(in_range ? idx_next[i] : 0) * (kDQK * 2);
+                    const int row = gather_row(idx_next[i], qm_next, p);
+                    nb[i] = row >= 0 ? 16u : 0u;
+                    src[i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
                 }
                 if (tile + 1 < n_tiles) load_idx(ql, tile + 1, idx_next);
                 else load_idx(ql + n_pairs, 0, idx_next);
@@ -970,15 +971,14 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         const char* kvb = reinterpret_cast<const char*>(p.kv) + chunk0 * 128 + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
         // the indices of a tile are loaded one tile ahead, so that their latency is never in front of the copies
-        // (already translated to the kv row to read, -1: read nothing)
+        // (raw values, turned into kv rows when they are used: nothing may depend on a load here)
         int idx_next[2];
         const QMeta qm = load_qmeta(p, qg);
         auto load_idx = [&](int tile) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int key = tile * kTileKeys + r0 + 32 * i;
-                idx_next[i] = (tile < n_tiles && key < p.topk)
-                                  ? gather_row(__ldg(p.indices + static_cast<size_t>(qg) * p.topk + key), qm, p) : -1;
+                idx_next[i] = (tile < n_tiles && key < p.topk) ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
             }
         };
         load_idx(0);
@@ -988,9 +988,9 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             uint32_t nb[2];   // 0: slot out of range, read nothing and land zeros (no shared stand-in row: it would be a hot spot)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const bool in_range = idx_next[i] >= 0;
-                nb[i] = in_range ? 16u : 0u;
-                src[i] = kvb + static_cast<size_t>(in_range ? idx_next[i] : 0) * (kDQK * 2);
+                const int row = gather_row(idx_next[i], qm, p);
+                nb[i] = row >= 0 ? 16u : 0u;
+                src[i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
             }
             load_idx(tile + 1);
             mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);

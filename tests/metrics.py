@@ -27,14 +27,19 @@ def error_figures(ref: torch.Tensor, got: torch.Tensor, chunk: int = 1 << 24) ->
 
 
 def assert_backward_close(dq, dkv, dq_ref, dkv_ref, what=""):
-    """The tolerances of tests/test_gpu_parity.py: the reference's gate rel_diff < 0.01, cosine > 0.99999,
-    max-abs <= 2^-7 max|ref| for dQ (compared with the bf16-rounded reference, one output rounding) and
-    <= 1e-3 max|ref| for dKV (fp32 atomics in arbitrary order over bf16-rounded S / dS)."""
+    """The reference's gate rel_diff < 0.01 (`mla_bwd/test_mla_bwd.py:191-193`), tightened with cosine > 0.99999,
+    max-abs <= 2^-7 max|ref| for dQ (compared with the bf16-rounded reference: one rounding step of the output) and
+    max-abs <= 2^-8 max|ref| for dKV.  Why 2^-8 and not less: oracle and kernel both round S and dS to bf16 before the
+    second-stage products, but reach the fp32 value being rounded by different routes (exp2 vs ex2.approx, different
+    summation order), so a value that sits on a rounding boundary can come out one bf16 step apart (the stage test
+    bounds how many do).  One such entry moves one element of dKV by 2^-8 |S| |dO|, i.e. by 2^-8 of a term that can
+    dominate that element when few queries touch the row; with thousands of queries per row the figure is far smaller
+    (the full-size tests print it)."""
     fq = error_figures(dq_ref.bfloat16().float(), dq.float())
     fk = error_figures(dkv_ref.reshape(dkv.shape).float(), dkv.float())
     msg = f"{what} dQ {fq} dKV {fk}"
     assert fq["rel_diff"] < 0.01 and fk["rel_diff"] < 0.01, msg
     assert fq["cosine"] > 0.99999 and fk["cosine"] > 0.99999, msg
     assert fq["max_abs"] <= 2 ** -7 * fq["max_ref"] + 1e-6, msg
-    assert fk["max_abs"] <= 1e-3 * fk["max_ref"] + 1e-6, msg
+    assert fk["max_abs"] <= 2 ** -8 * fk["max_ref"] + 1e-6, msg
     return fq, fk

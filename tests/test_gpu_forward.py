@@ -77,3 +77,43 @@ def test_forward_full_size_query_subset():
     o, lse = op.mla_fwd(s["q"], s["kv"], s["indices"], q_start_index_s=None, check_device_status=True)
     assert torch.allclose(lse.cpu(), lse_ref * LOG2E, rtol=0, atol=3e-4)
     assert cosine(o.float().cpu(), o_ref) > 0.9999
+
+
+@pytest.mark.parametrize("name", ["dqphase_full_topk_window", "dqphase_partial_causal_window"])
+def test_forward_and_natural_log_backward_against_reference_phase_test_golden(name):
+    """Vectors made by the reference's phase-test checker (`dq_test/test_dq_phase.py:39-66`, see
+    tests/golden/make_golden_fwd.py): the forward's o / lse, and - fed with that natural-log lse, that o and the query
+    start - the backward's S, dS (stage check) and dQ.  Its two cases: query start 63 and 0, [s_kv, 1, 576] kv and
+    [s_q, 1, topk] indices, out-of-range sentinel s_kv."""
+    import os
+    import numpy as np
+    from oracle.sparse_mla_ref import calc_diff
+    from tests.golden.make_golden_fwd import make_fwd_case_inputs
+    from test_operator_b200 import op
+    q, kv, dO, indices, q_start = make_fwd_case_inputs(name)
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", f"{name}.npz"))
+    rows = torch.from_numpy(g["rows"]).long()
+    qd, kvd, dOd, idxd = q.to(DEV), kv.to(DEV), dO.to(DEV), indices.to(DEV)
+    o, lse = op.mla_fwd(qd, kvd, idxd, q_start_index_s=q_start, lse_is_base2=False, check_device_status=True)
+    assert torch.allclose(lse.cpu(), torch.from_numpy(g["lse"]), rtol=0, atol=2e-4)
+    o_gold = torch.from_numpy(g["o_bits"]).view(torch.bfloat16).float()
+    assert (o[rows.to(DEV)].float().cpu() - o_gold).abs().max().item() <= 2 ** -6 * o_gold.abs().max().item()
+    assert cosine(o[rows.to(DEV)].float().cpu(), o_gold) > 0.9999
+    # backward with the golden forward outputs (all 32 queries come from the restated forward, pinned bit for bit to
+    # the reference on CPU; the stored rows are the ones compared)
+    o_ref, lse_ref = sparse_mla_fwd_ref(q, kv.squeeze(1), indices.squeeze(1), q_start_index_s=q_start)
+    ws = op.workspace_for(qd, kvd, idxd)
+    dq = torch.empty_like(qd)
+    dkv = torch.empty(kvd.shape, dtype=torch.float32, device=DEV)
+    lay = op.run_stages(qd, kvd, dOd, lse_ref.to(DEV), o_ref.to(DEV), idxd, dq, dkv, ws, op.STAGE_ALL,
+                        q_start_index_s=q_start, lse_is_base2=False)
+    assert op.device_status(ws) == 0
+    dq_gold = torch.from_numpy(g["dQ_bits"]).view(torch.bfloat16).float()
+    mx, rel = calc_diff(dq_gold, dq[rows.to(DEV)].float().cpu())
+    assert rel < 1e-2 and cosine(dq_gold, dq[rows.to(DEV)].float().cpu()) > 0.99999      # the phase test's own gate is rel < 1e-2
+    S, dS = (m.cpu() for m in op.scratch_matrices(ws, lay))
+    S_gold = torch.from_numpy(g["S_bits"]).view(torch.bfloat16).float().transpose(1, 2)      # [query, slot, head]
+    dS_gold = torch.from_numpy(g["dS_bits"]).view(torch.bfloat16).float().transpose(1, 2)
+    for mine, gold in ((S[rows, :64, :128].float(), S_gold), (dS[rows, :64, :128].float(), dS_gold)):
+        err = (mine - gold).abs()
+        assert torch.all(err <= 2 ** -7 * gold.abs() + 2e-4 * gold.abs().max())

@@ -12,7 +12,7 @@ DEV = "cuda:0"
 KEYS = ("q", "kv", "dO", "lse", "O", "indices")
 
 
-@pytest.mark.parametrize("chunks,dkv_pairs", [(3, 24), (4, 40)])
+@pytest.mark.parametrize("chunks,dkv_pairs", [(2, 0), (3, 24), (4, 40)])
 def test_overlapped_schedule_matches_sequential_and_oracle(chunks, dkv_pairs):
     from test_operator_b200 import op
     # enough queries that every part keeps all clusters busy (the library falls back to fewer parts otherwise)
@@ -40,3 +40,34 @@ def test_overlapped_schedule_matches_sequential_and_oracle(chunks, dkv_pairs):
         op.set_schedule(*before)
     dq_ref, dkv_ref = sparse_mla_bwd_ref(*args, q_start_index_s=None, chunk_s=16)
     assert_backward_close(dq1, dkv1, dq_ref, dkv_ref, "overlapped")
+
+
+def test_default_schedule_overlaps_and_replays_from_a_cuda_graph():
+    """The library's default is the overlapped schedule; its second stream forks from and joins the caller's stream, so
+    a capture of the caller's stream takes the whole call (the first call, which creates that stream, came before)."""
+    from test_operator_b200 import op
+    assert op.get_schedule()[0] >= 2
+    w = Workload("sched_graph", 1, 1400, 2048, 128, 256, "uniform", invalid_frac=0.1)
+    s = make_sequence(w, device=DEV, seed=38)
+    args = [s[k] for k in KEYS]
+    ws = op.workspace_for(s["q"], s["kv"], s["indices"])
+    dkv = torch.empty(s["kv"].shape, dtype=torch.float32, device=DEV)
+    dq_eager, _ = op.mla_bwd(*args, q_start_index_s=None, out_dkv=dkv, workspace=ws)
+    assert op.last_launch_count() == 1 + 3 * op.get_schedule()[0]
+    dkv_eager = dkv.clone()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            dq_g, _ = op.mla_bwd(*args, q_start_index_s=None, out_dkv=dkv, workspace=ws)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        dkv.fill_(7.0)
+        dq_g.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert op.device_status(ws) == 0
+        assert torch.equal(dq_g.view(torch.int16), dq_eager.view(torch.int16))
+        assert (dkv - dkv_eager).abs().max().item() <= 1e-5 * dkv_eager.abs().max().item()

@@ -85,3 +85,27 @@ def test_workload_index_generators():
         for r in range(8):
             v = idx[r][(idx[r] >= 0) & (idx[r] < small.s_kv)]
             assert v.unique().numel() == v.numel(), "valid indices of a query must be distinct"
+
+
+@pytest.mark.parametrize("name", sorted(__import__("tests.golden.make_golden_fwd", fromlist=["FWD_CASES"]).FWD_CASES))
+def test_forward_oracle_matches_reference_phase_test_golden(name):
+    """o / lse of the restated forward, and S / dS / dQ of the restated backward fed with natural-log lse and a query
+    start, against what the reference's phase-test checker (`dq_test/test_dq_phase.py:39-66`) produced."""
+    from tests.golden.make_golden_fwd import make_fwd_case_inputs
+    q, kv, dO, indices, q_start = make_fwd_case_inputs(name)
+    g = np.load(os.path.join(GOLD, f"{name}.npz"))
+    rows = torch.from_numpy(g["rows"]).long()
+    o, lse = sparse_mla_fwd_ref(q, kv.squeeze(1), indices.squeeze(1), q_start_index_s=q_start)
+    assert (lse - torch.from_numpy(g["lse"])).abs().max().item() <= 1e-4
+    o_gold = torch.from_numpy(g["o_bits"]).view(torch.bfloat16)
+    assert (o[rows].view(torch.int16) != o_gold.view(torch.int16)).float().mean().item() <= 1e-3
+    dq, _, _, S, dS = sparse_mla_bwd_ref(q, kv.squeeze(1), dO, lse, o, indices.squeeze(1), q_start_index_s=q_start,
+                                         lse_is_base2=False, return_intermediates=True)
+    dq_gold = torch.from_numpy(g["dQ_bits"]).view(torch.bfloat16).float()
+    assert calc_diff(dq_gold, dq[rows])[1] < 1e-2 and cosine(dq_gold, dq[rows]) > 0.9999
+    # the reference keeps S / dS as [query, head, slot]; the oracle's intermediates are [query, slot, head]
+    S_gold = torch.from_numpy(g["S_bits"]).view(torch.bfloat16).float().transpose(1, 2)
+    dS_gold = torch.from_numpy(g["dS_bits"]).view(torch.bfloat16).float().transpose(1, 2)
+    for mine, gold in ((S[rows].float(), S_gold), (dS[rows].float(), dS_gold)):
+        err = (mine - gold).abs()
+        assert torch.all(err <= 2 ** -7 * gold.abs() + 2e-4 * gold.abs().max())
