@@ -126,6 +126,8 @@ def _dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # the pull-reduce reads peers with plain loads only; no multicast object is bound to its buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return rank, world, local
@@ -272,6 +274,30 @@ def _query_sharded_block(op, sharding, dist, rank, world, dev, steps, warmup):
     out_rows = torch.empty(k1 - k0, 576, dtype=torch.float32, device=dev)
     flat = partial.reshape(w.s_kv, 576)
     ms_coll = timed(lambda: dist.reduce_scatter_tensor(out_rows, flat, op=dist.ReduceOp.SUM), 10)
+    # ---- the same step with the library's NVLink pull-reduce in place of NCCL (partials in symmetric memory, cleared by
+    # the reduction itself, so the backward accumulates and no memset runs)
+    pull = None
+    try:
+        reducer = sharding.PullReducer(w.s_kv, dev)
+    except Exception as e:          # symmetric memory unavailable on this box: say so, NCCL figures stand
+        pull = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    else:
+        def pull_step():
+            return sharding.query_sharded_bwd(op.mla_bwd, mine["q"], kv, mine["dO"], mine["lse"], mine["O"], mine["indices"],
+                                              r0, qs, reducer=reducer, workspace=ws)
+        _, rows_nccl = step()
+        _, rows_pull = pull_step()
+        torch.cuda.synchronize()
+        d = torch.tensor([(rows_pull - rows_nccl).abs().max().item(), rows_nccl.abs().max().item()], dtype=torch.float64, device=dev)
+        dist.all_reduce(d, op=dist.ReduceOp.MAX)
+        for _ in range(2):
+            pull_step()
+        ms_pull = timed(pull_step, steps)
+        ms_pull_coll = timed(lambda: reducer.reduce(out_rows), 10)
+        pull = {"ms_per_step": ms_pull, "value": 5504.0 * w.s_q * w.h_q * w.topk / (ms_pull * 1e-3) / 1e12,
+                "collective_ms": ms_pull_coll, "max_abs_vs_nccl": d[0].item(), "max_ref": d[1].item(),
+                "how": "smla_dkv_pull_reduce between two symmetric-memory barriers; plain peer loads, sources cleared in the same kernel"}
+        del reducer
     status = torch.tensor([op.device_status(ws)], dtype=torch.int64, device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)
     # ---- the same workload on one GPU (rank 0 alone; the others wait): the base the scaling is measured against
@@ -296,7 +322,7 @@ def _query_sharded_block(op, sharding, dist, rank, world, dev, steps, warmup):
            "ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
            "compute_ms": ms_compute, "collective_ms": ms_coll,
            "collective": f"ncclReduceScatter (torch reduce_scatter_tensor) of the {w.s_kv * 576 * 4 / 1e6:.0f} MB fp32 partial dKV, timed alone",
-           "check": check, "device_status": int(status.item())}
+           "check": check, "pull_reduce": pull, "device_status": int(status.item())}
     if base_ms is not None:
         blk["scaling_base"] = {"ms_per_step": base_ms, "value": flops / (base_ms * 1e-3) / 1e12, "n_gpus": 1,
                                "speedup": base_ms / ms}

@@ -184,6 +184,18 @@ void smla_bwd_get_schedule(int* chunks, int* dkv_pairs);
 int smla_debug_set_wait_limit_cycles(long long cycles);
 int smla_selftest_wait_timeout(void* workspace, int which, long long limit_cycles, long long* out3, void* stream);
 
+/* Query-sharded runs (one long sequence, queries split over `world` GPUs of one node, every rank holding a full-size
+ * fp32 partial dKV): sum the partials' rows [rank * s_kv / world, (rank + 1) * s_kv / world) into `out`
+ * ([s_kv / world, 576] fp32, this GPU's memory).  `partials[r]` is rank r's partial buffer as mapped into THIS process
+ * (its own for r == rank, peer mappings otherwise; `partials` itself is a host array).  The kernel reads peers with
+ * plain loads over NVLink and adds in rank order.  With zero_sources != 0 it clears what it has read, in every
+ * rank's buffer, so that after all ranks have run it every partial is zero for the next step.  The caller must order
+ * it between two cross-rank barriers on the stream (all partials complete before; nobody reuses a partial before
+ * everyone has finished).  No counterpart in the reference, which has no multi-GPU code; it stands in for
+ * ncclReduceScatter on this path. */
+int smla_dkv_pull_reduce(const void* const* partials, int32_t world, int32_t rank, int32_t s_kv, float* out,
+                         int32_t zero_sources, void* stream);
+
 /* Measurement aid: every SM that gets a block writes {its cycle counter, the global nanosecond timer} to
  * out[2 * smid], out[2 * smid + 1] (device memory, 2 * n_sm x u64; SMs that got none keep what was there).  Two probes
  * around a timed region give the average SM clock inside it: delta cycles / delta ns per SM. */

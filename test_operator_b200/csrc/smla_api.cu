@@ -716,6 +716,71 @@ int smla_index_inverse(const int32_t* indices, int32_t s_q, int32_t topk, int32_
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
 }
 
+// ---- sum of the ranks' partial dKV over NVLink (query-sharded runs) ---------------------------------------------
+// Rank r owns kv rows [r * rows, (r + 1) * rows).  Every CTA walks a slice of the owned rows, loads the same 16 bytes
+// from every rank's partial buffer (its own from HBM, the others' through NVLink with plain loads: no TMA, no
+// multicast), adds them in rank order (so the result does not depend on timing) and stores the sum.  With
+// `zero_sources` it also writes zeros back over what it has read, in every rank's buffer: each row of every partial
+// is read by exactly one rank, its owner, so after all ranks have run the kernel every partial is clear for the next
+// step and no separate memset is needed.  The caller orders the kernel between two cross-rank barriers.
+namespace {
+constexpr int kMaxRanks = 16;
+struct PeerPtrs {
+    float4* p[kMaxRanks];
+};
+__global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs peers, int world, int rank, float4* __restrict__ out,
+                                                          size_t n4, size_t first4, int zero_sources) {
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 v[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < world) v[r] = peers.p[r][first4 + i];
+        float4 acc = v[0];
+#pragma unroll
+        for (int r = 1; r < kMaxRanks; ++r)
+            if (r < world) {
+                acc.x += v[r].x;
+                acc.y += v[r].y;
+                acc.z += v[r].z;
+                acc.w += v[r].w;
+            }
+        out[i] = acc;
+        if (zero_sources) {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world) peers.p[r][first4 + i] = zero;
+        }
+    }
+}
+}  // namespace
+
+int smla_dkv_pull_reduce(const void* const* partials, int32_t world, int32_t rank, int32_t s_kv, float* out,
+                         int32_t zero_sources, void* stream) {
+    if (!partials || !out || world < 1 || world > kMaxRanks || rank < 0 || rank >= world || s_kv <= 0 || s_kv % world)
+        return SMLA_ERR_BAD_ARG;
+    PeerPtrs pp{};
+    for (int r = 0; r < world; ++r) {
+        if (!partials[r] || !aligned16(partials[r])) return SMLA_ERR_BAD_ARG;
+        pp.p[r] = reinterpret_cast<float4*>(const_cast<void*>(partials[r]));
+    }
+    if (!aligned16(out)) return SMLA_ERR_BAD_ARG;
+    const size_t rows = static_cast<size_t>(s_kv) / world;
+    const size_t n4 = rows * (SMLA_D_QK / 4);
+    const size_t first4 = static_cast<size_t>(rank) * n4;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return SMLA_ERR_LAUNCH;
+    size_t blocks = (n4 + 255) / 256;
+    const size_t cap = static_cast<size_t>(sms) * 8;
+    if (blocks > cap) blocks = cap;
+    pull_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        pp, world, rank, reinterpret_cast<float4*>(out), n4, first4, zero_sources);
+    g_last_launches = 1;
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
+
 // ---- SM clock probe ------------------------------------------------------------------------------------------
 namespace {
 __global__ void clock_probe_kernel(unsigned long long* out, int n_sm) {

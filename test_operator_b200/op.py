@@ -130,6 +130,9 @@ def load_library() -> ctypes.CDLL:
         lib.smla_selftest_wait_timeout.restype = ctypes.c_int
         lib.smla_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p,
                                                    ctypes.c_void_p]
+        lib.smla_dkv_pull_reduce.restype = ctypes.c_int
+        lib.smla_dkv_pull_reduce.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                             ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
         lib.smla_clock_probe.restype = ctypes.c_int
         lib.smla_clock_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.smla_bwd_status_string = lib.smla_status_string
