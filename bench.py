@@ -492,7 +492,7 @@ def run_ours(args):
             roofline["traffic_source"] = TRAFFIC_SOURCE[dom] + " (296-query ncu capture, scaled by the number of queries)"
         # the whole step against the same peak, and where its time goes in SM cycles
         step_tf = flops / (ms * 1e-3) / 1e12
-        roofline["step"] = {"achieved": step_tf, "frac": step_tf / peak}
+        roofline["step"] = {"achieved_per_gpu": step_tf / world, "frac": step_tf / world / peak}
         if step_mhz and all("mcycles" in v for v in kernels.values()) and world == 1 and len(seqs) == 1:
             kc = sum(v["mcycles"] for v in kernels.values())
             roofline["step"].update({"sm_mhz": step_mhz, "mcycles": ms * step_mhz * 1e-3, "kernels_alone_mcycles": kc,

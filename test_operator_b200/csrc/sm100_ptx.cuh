@@ -304,8 +304,14 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 // call, which a thread relaying one signal per pipeline step cannot afford.  Only for signals whose data is
 // already in place by other means: shared memory of the signalling CTA filled by copies this thread has seen
 // complete (and fenced to the async proxy), or tensor-memory reads this warp has waited for.
+// The PTX memory model promises this ordering only for the release form; that the relaxed form is enough here rests
+// on the two cases above and on measurement (a build with -DSMLA_RELEASE_ARRIVE gives bit-identical S, dS and dQ).
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+#ifdef SMLA_RELEASE_ARRIVE
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#else
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#endif
 }
 __device__ __forceinline__ void tmem_alloc_2cta(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)

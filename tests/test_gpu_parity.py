@@ -261,3 +261,30 @@ def test_full_size_head128_properties():
     got = dkv_s.sum(0)
     assert cosine(want.cpu(), got.cpu()) > 0.9999
     assert (want - got).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
+def test_back_to_back_runs_repeat_bit_for_bit():
+    """Twenty runs of a case with more queries than resident clusters (every cluster walks through several queries,
+    the pipelines never drain in between): S, dS and dQ must come out bit-identical every time.  The hand-overs between
+    the two CTAs of a cluster use relaxed cluster-scope arrivals (the release form costs hundreds of cycles per
+    call); a stale read there would show up as a rare difference between runs."""
+    op = _op()
+    w = Workload("repeat", 1, 700, 1024, 128, 512, "uniform", invalid_frac=0.1)
+    seq = make_sequence(w, device=DEV, seed=77)
+    q, kv, dO, lse, O, idx = (seq[k] for k in ("q", "kv", "dO", "lse", "O", "indices"))
+    ws = op.workspace_for(q, kv, idx)
+    dq = torch.empty_like(q)
+    dkv = torch.empty(kv.shape, dtype=torch.float32, device=DEV)
+    first = None
+    for _ in range(20):
+        lay = op.run_stages(q, kv, dO, lse, O, idx, dq, dkv, ws, op.STAGE_ALL, q_start_index_s=None)
+        S, dS = op.scratch_matrices(ws, lay)
+        cur = (S.clone(), dS.clone(), dq.clone())
+        if first is None:
+            first = cur
+        else:
+            for a, b in zip(first, cur):
+                assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert op.device_status(ws) == 0
+    ref = sparse_mla_bwd_ref(q, kv, dO, lse, O, idx, q_start_index_s=None, chunk_s=16)
+    _assert_close(dq, dkv, ref[0].cpu(), ref[1].cpu())
