@@ -40,7 +40,7 @@ KERNEL_NAMES = {"recompute": "smla_recompute_pair_kernel", "dkv": "smla_dkv_pair
 # profiles/ (296-query case, dram__bytes_read.sum + dram__bytes_write.sum divided by 296; every kernel's DRAM
 # traffic grows in proportion to the number of queries).  They describe the kernels as captured there: a kernel
 # change needs a new capture, and `roofline.traffic_source` names the summary the figure came from.
-DRAM_BYTES_PER_QUERY_H128_TOPK2048 = {"recompute": 1.360e6, "dkv": 2.228e6, "dq": 0.703e6}
+DRAM_BYTES_PER_QUERY_H128_TOPK2048 = {"recompute": 1.366e6, "dkv": 2.248e6, "dq": 0.722e6}
 TRAFFIC_SOURCE = {"recompute": "profiles/smla_recompute_pair_kernel_head128_296q.txt",
                   "dkv": "profiles/smla_dkv_pair_kernel_head128_296q.txt", "dq": "profiles/smla_dq_kernel_head128_296q.txt"}
 # share of the 5504 FLOPs per slot each kernel carries: recompute = P + dP, dkv = dV + dK, dq = dQ
