@@ -363,6 +363,17 @@ __device__ __forceinline__ void st_global_v8(void* addr, const uint32_t (&v)[8])
 }
 
 // ---- small helpers -----------------------------------------------------------------------------
+// Integer reductions over the 32 lanes of a warp in one instruction (every lane receives the result).
+__device__ __forceinline__ int redux_max_s32(int v) {
+    int r;
+    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ unsigned redux_add_u32(unsigned v) {
+    unsigned r;
+    asm volatile("redux.sync.add.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+    return r;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

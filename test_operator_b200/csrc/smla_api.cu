@@ -263,7 +263,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     if (!ok) return SMLA_ERR_LAUNCH;
 
     // per device, so set on every call (cheap) rather than once per process
-    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, false>, rp::Cfg<HP, false>::kSmemBytes);
+    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, 0>, rp::Cfg<HP, 0>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_pair_kernel<HP>, dp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dq_kernel<HP, kSplitChunk, kQChunks>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
@@ -299,11 +299,11 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
                                                           reinterpret_cast<const uint4*>(p->dO), delta, n_rows);
         ++g_last_launches;
     }
-    const int pairs_r = resident_pairs(smla_recompute_pair_kernel<HP, false>, rp::kThreads, rp::Cfg<HP, false>::kSmemBytes);
+    const int pairs_r = resident_pairs(smla_recompute_pair_kernel<HP, 0>, rp::kThreads, rp::Cfg<HP, 0>::kSmemBytes);
     const int pairs_d = resident_pairs(smla_dkv_pair_kernel<HP>, dp::kThreads, dp::Cfg<HP>::kSmemBytes);
     if (pairs_r <= 0 || pairs_d <= 0) return SMLA_ERR_LAUNCH;
     auto launch_recompute = [&](cudaStream_t s_, int pairs) {
-        smla_recompute_pair_kernel<HP, false><<<2 * (kp.nq < pairs ? kp.nq : pairs), rp::kThreads, rp::Cfg<HP, false>::kSmemBytes, s_>>>(tm_qnh, tm_donh, kp);
+        smla_recompute_pair_kernel<HP, 0><<<2 * (kp.nq < pairs ? kp.nq : pairs), rp::kThreads, rp::Cfg<HP, 0>::kSmemBytes, s_>>>(tm_qnh, tm_donh, kp);
         ++g_last_launches;
     };
     auto launch_dkv = [&](cudaStream_t s_, int pairs) {
@@ -364,9 +364,10 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- forward ---------------------------------------------------------------------------------------------
+// Workspace: error word | row maxima [s_q, h_q] i32 | row sums [s_q, h_q] u64 | E scratch (bf16, one matrix per query).
 struct FwdPlan {
     int h_pad, topk_pad, q_chunk;
-    size_t err_off, logits_off, s_off, total;
+    size_t err_off, m_off, l_off, s_off, total;
 };
 
 bool check_fwd_params(const smla_fwd_params* p) {
@@ -378,43 +379,50 @@ bool check_fwd_params(const smla_fwd_params* p) {
     return true;
 }
 
+void fwd_layout(const smla_fwd_params* p, FwdPlan* pl, size_t qc) {
+    const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;   // one bf16 matrix per query
+    const size_t rows = size_t(p->s_q) * p->h_q;
+    pl->q_chunk = int(qc);
+    pl->err_off = 0;
+    pl->m_off = kAlign;
+    pl->l_off = align_up(pl->m_off + rows * 4, kAlign);
+    pl->s_off = align_up(pl->l_off + rows * 8, kAlign);
+    pl->total = align_up(pl->s_off + qc * unit, kAlign);
+}
+
 bool make_fwd_plan(const smla_fwd_params* p, size_t budget, FwdPlan* pl) {
     if (!check_fwd_params(p)) return false;
     pl->h_pad = p->h_q <= 64 ? 64 : 128;
     pl->topk_pad = (p->topk + 255) / 256 * 256;
-    const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;   // one bf16 matrix per query
-    const size_t per_q = 3 * unit;                              // fp32 logits + bf16 S
+    const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;
     if (budget == 0) budget = kDefaultBudget;
-    size_t qc = budget > kAlign ? (budget - kAlign) / per_q : 0;
+    fwd_layout(p, pl, 1);
+    const size_t fixed = pl->s_off;
+    size_t qc = budget > fixed ? (budget - fixed) / unit : 0;
     if (qc < 1) qc = 1;
     if (qc > size_t(p->s_q)) qc = p->s_q;
     while (qc > 1 && qc * size_t(pl->topk_pad) > size_t(INT_MAX)) qc /= 2;
-    pl->q_chunk = int(qc);
-    pl->err_off = 0;
-    pl->logits_off = kAlign;
-    pl->s_off = align_up(pl->logits_off + qc * 2 * unit, kAlign);
-    pl->total = align_up(pl->s_off + qc * unit, kAlign);
+    fwd_layout(p, pl, qc);
     return true;
 }
 
 bool fwd_plan_for_workspace(const smla_fwd_params* p, size_t ws_bytes, FwdPlan* pl) {
     if (!make_fwd_plan(p, ws_bytes, pl)) return false;
+    const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;
     while (pl->total > ws_bytes && pl->q_chunk > 1) {
-        const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;
         const size_t over = pl->total - ws_bytes;
-        int dec = int(over / (3 * unit)) + 1;
-        const int qc = pl->q_chunk - dec < 1 ? 1 : pl->q_chunk - dec;
-        pl->q_chunk = qc;
-        pl->s_off = align_up(pl->logits_off + size_t(qc) * 2 * unit, kAlign);
-        pl->total = align_up(pl->s_off + size_t(qc) * unit, kAlign);
+        const int dec = int(over / unit) + 1;
+        fwd_layout(p, pl, pl->q_chunk - dec < 1 ? 1 : pl->q_chunk - dec);
     }
     return pl->total <= ws_bytes;
 }
 
+// Three passes over the queries: row maxima of the logits (nothing but 4 bytes per row is written); E = exp2(logit -
+// max) as bf16 into the scratch plus its row sums; o = E.V divided by the sum on the way out, and lse.  The logits are
+// computed twice (576 of the forward's 1088 multiply-adds per slot) in exchange for never existing in memory.
 template <int HP>
 int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, cudaStream_t st) {
     using namespace smla;
-    float* logits = reinterpret_cast<float*>(ws + pl.logits_off);
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
     CUtensorMap tm_qnh, tm_s;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
@@ -422,16 +430,18 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
     ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
-    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, true>, rp::Cfg<HP, true>::kSmemBytes);
-    // o = S.V: the two d-parts gather V column chunks [0,4) and [4,8)
-    attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks>, dq::Cfg<HP>::kSmemBytes);
+    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, 1>, rp::Cfg<HP, 1>::kSmemBytes);
+    attr_ok &= set_smem(smla_recompute_pair_kernel<HP, 2>, rp::Cfg<HP, 2>::kSmemBytes);
+    // o = E.V: the two d-parts gather V column chunks [0,4) and [4,8)
+    attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks, true>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
     KParams kp{};
     kp.kv = reinterpret_cast<const __nv_bfloat16*>(p->kv);
     kp.indices = p->indices;
     kp.s_scr = s_scr;
-    kp.logits = logits;
+    kp.m_ord = reinterpret_cast<int*>(ws + pl.m_off);
+    kp.l_fix = reinterpret_cast<unsigned long long*>(ws + pl.l_off);
     kp.lse_out = p->lse;
     kp.lse_out_mult = p->lse_is_base2 ? 1.0f : 0.6931471805599453f;
     kp.g_err = reinterpret_cast<int*>(ws + pl.err_off);
@@ -448,15 +458,19 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     kp.qmeta = reinterpret_cast<const int4*>(p->query_meta);
     kp.wait_limit = g_wait_limit.load();
     kp.scr0 = 0;
+    const int n_rows = p->s_q * p->h_q;
+    smla_fwd_stats_init_kernel<<<(n_rows + 255) / 256, 256, 0, st>>>(kp.m_ord, kp.l_fix, n_rows);
+    ++g_last_launches;
+    const int pairs = resident_pairs(smla_recompute_pair_kernel<HP, 1>, rp::kThreads, rp::Cfg<HP, 1>::kSmemBytes);
+    if (pairs <= 0) return SMLA_ERR_LAUNCH;
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         kp.nq = nq;
-        const int pairs = resident_pairs(smla_recompute_pair_kernel<HP, true>, rp::kThreads, rp::Cfg<HP, true>::kSmemBytes);
-        if (pairs <= 0) return SMLA_ERR_LAUNCH;
-        smla_recompute_pair_kernel<HP, true><<<2 * (nq < pairs ? nq : pairs), rp::kThreads, rp::Cfg<HP, true>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
-        smla_fwd_softmax_kernel<HP><<<nq, 512, 0, st>>>(kp);
-        smla_dq_kernel<HP, kVChunks / 2, kVChunks><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_s, kp);
+        const int grid = 2 * (nq < pairs ? nq : pairs);
+        smla_recompute_pair_kernel<HP, 1><<<grid, rp::kThreads, rp::Cfg<HP, 1>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
+        smla_recompute_pair_kernel<HP, 2><<<grid, rp::kThreads, rp::Cfg<HP, 2>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
+        smla_dq_kernel<HP, kVChunks / 2, kVChunks, true><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_s, kp);
         g_last_launches += 3;
     }
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;

@@ -40,7 +40,8 @@ struct KParams {
     float* dKV;               // [s_kv, 576]
     __nv_bfloat16* dQ;        // [s_q, h_q, 576]
     // forward only
-    float* logits;            // [q_chunk][topk_pad keys][HP heads] base-2 logits, -inf where masked
+    int* m_ord;               // [s_q, h_q] row maximum of the raw logits Q.K, as order-preserving integers
+    unsigned long long* l_fix;// [s_q, h_q] row sum of exp2(logit - max) in 2^-24 fixed point
     float* lse_out;           // [s_q, h_q]
     float lse_out_mult;       // 1 (base 2) or ln 2 (natural log)
     // dq-style kernel: where the result goes (dQ with pitch 576, or o with pitch 512)
@@ -97,6 +98,18 @@ enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300 };
 __device__ __forceinline__ bool slot_valid(int idx, int key, const QMeta& m, const KParams& p) {
     return key < m.topk_len && idx >= 0 && idx < m.kv_len && m.kv_base + idx < p.s_kv && (!p.causal || idx <= m.q_pos);
 }
+
+// fp32 <-> integers that compare like the floats they came from (so that integer max instructions and atomics work
+// on them); -inf maps to the smallest value used
+__device__ __forceinline__ int float_to_ordered(float x) {
+    const int i = __float_as_int(x);
+    return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float ordered_to_float(int o) {
+    return __int_as_float(o ^ ((o >> 31) & 0x7fffffff));
+}
+constexpr int kOrderedNegInf = static_cast<int>(0xff800000u ^ 0x7fffffffu);   // float_to_ordered(-inf)
+constexpr float kFixScale = 16777216.f;                                          // 2^24
 
 // =============================================================================================
 // Delta = rowsum(O * dO).  One warp per (query, head) row of 512 bf16; each lane reads 2 x 16 B
@@ -157,10 +170,12 @@ constexpr int kThreads = 608;
 constexpr int kProducerThreads = 256;
 constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;         // 16 KB gathered chunk
-// kFwd = false: backward recompute (B = [Q | dO], outputs bf16 S and dS)
-// kFwd = true : forward logits     (B = Q only, outputs fp32 base-2 logits); the shared memory dO would
-//               take goes to a deeper gather ring
-template <int HP, bool kFwd> struct Cfg {
+// kMode 0: backward recompute (B = [Q | dO], outputs bf16 S and dS)
+// kMode 1: forward, first pass  (B = Q only): row maxima of the logits, nothing else is written
+// kMode 2: forward, second pass (B = Q only): E = exp2(logit - max) as bf16 into the S scratch, and its row sums
+// In the forward passes the shared memory dO would take goes to a deeper gather ring.
+template <int HP, int kMode> struct Cfg {
+    static constexpr bool kFwd = kMode != 0;
     static constexpr int NH = HP / 2;                  // heads whose Q / dO rows this CTA holds
     static constexpr int kStages = kFwd ? 9 : 5;
     static constexpr int kBHalf = NH * 128;            // one [NH heads x 64 col] chunk
@@ -174,12 +189,13 @@ template <int HP, bool kFwd> struct Cfg {
 };
 }  // namespace rp
 
-template <int HP, bool kFwd>
+template <int HP, int kMode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(rp::kThreads, 1)
 smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                            const KParams p) {
     using namespace rp;
-    using C = Cfg<HP, kFwd>;
+    using C = Cfg<HP, kMode>;
+    constexpr bool kFwd = kMode != 0;
     constexpr int NH = C::NH;
     constexpr int kStages = C::kStages;
     const uint32_t rank = cluster_ctarank();
@@ -418,12 +434,14 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         // lse (threads 0..HP-1) and Delta (threads HP..2HP-1) of a query go through shared memory; the value for
         // the next query is fetched one query ahead
         const int t = threadIdx.x;
+        // (forward, second pass: the row maximum found by the first pass takes the place of lse, in base-2 units)
         auto load_stat = [&](int ql) -> float {
-            if (kFwd || ql >= nq) return 0.f;
+            if (kMode == 1 || ql >= nq) return 0.f;
             const int h = t < HP ? t : t - HP;
             if (t >= 2 * HP) return 0.f;
             if (h >= p.h_q) return t < HP ? __int_as_float(0x7f800000) : 0.f;
             const size_t o = static_cast<size_t>(p.q0 + ql) * p.h_q + h;
+            if constexpr (kMode == 2) return t < HP ? ordered_to_float(p.m_ord[o]) * p.scale_log2e : 0.f;
             return t < HP ? p.lse[o] * p.lse_mult : p.delta[o] * p.sm_scale;
         };
         float stat_next = load_stat(pair);
@@ -431,12 +449,15 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         for (int ql = pair; ql < nq; ql += n_pairs) {
             const int qg = p.q0 + ql;
             const QMeta qm = load_qmeta(p, qg);
-            if constexpr (!kFwd) {
+            if constexpr (kMode != 1) {
                 asm volatile("bar.sync 1, 256;" ::: "memory");      // every softmax warp is done with the previous query
                 if (t < 2 * HP) lse_s[t] = stat_next;              // delta_s follows lse_s
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 stat_next = load_stat(ql + n_pairs);
             }
+            // forward: what this lane keeps for heads g * NH + lane and g * NH + 32 + lane over the query's tiles
+            int keep_max[2] = {kOrderedNegInf, kOrderedNegInf};
+            unsigned long long keep_sum[2] = {0ull, 0ull};
             for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
                 const int key = tile * kTileKeys + rank * 128 + row;
                 const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
@@ -444,26 +465,67 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const int b = gt & 1;
                 mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
                 tc_fence_after_sync();
-                if constexpr (kFwd) {
-                    const size_t off = (static_cast<size_t>(p.scr0 + ql) * p.topk_pad + key) * HP + g * NH;
-                    // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order
+                if constexpr (kMode == 1) {
+                    // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order.  The maximum
+                    // over the warp's 32 keys of every head comes from one integer warp reduction per head.
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
-                    float* t_out = p.logits + off;
                     const float ninf = __int_as_float(0xff800000);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < NH; c0 += 32) {
+                        uint32_t pv[32];
+                        tmem_ld_32x32(taddr + c0, pv);
+                        tmem_ld_wait();
+                        int mine = kOrderedNegInf;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const int r = redux_max_s32(float_to_ordered(valid ? __uint_as_float(pv[c]) : ninf));
+                            if (lane == c) mine = r;
+                        }
+                        if (c0 == 0) keep_max[0] = max(keep_max[0], mine);
+                        else keep_max[1] = max(keep_max[1], mine);
+                    }
+                } else if constexpr (kMode == 2) {
+                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
+                    const size_t off = static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
+                    __nv_bfloat16* s_out = p.s_scr + off;
+                    const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
 #pragma unroll 1
                     for (int c0 = 0; c0 < NH; c0 += 16) {
                         uint32_t pv[16];
                         tmem_ld_32x16(taddr + c0, pv);
                         tmem_ld_wait();
-                        uint32_t lo[8], hi[8];
+                        uint32_t so[8];
+                        const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);
+                        unsigned mine = 0;
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const bool keep = valid && (g * NH + c0 + c) < p.h_q;
-                            const float tv = keep ? __uint_as_float(pv[c]) * p.scale_log2e : ninf;
-                            if (c < 8) lo[c] = __float_as_uint(tv); else hi[c - 8] = __float_as_uint(tv);
+                        for (int v = 0; v < 4; ++v) {
+                            const float4 l = l4[v];
+                            const float lv[4] = {l.x, l.y, l.z, l.w};
+                            float sv[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int c = 4 * v + e;
+                                // E <= 1 (+ one rounding): the same logits produced the maximum in the first pass
+                                const float ex = ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e]));
+                                sv[e] = ex;
+                                // row sums in 2^-24 fixed point: integer warp reductions and integer atomics add in
+                                // any order to the same result, and 2048 terms lose at most 2^-13 of a sum >= 1
+                                const unsigned fx = valid ? __float2uint_rz(ex * kFixScale) : 0u;
+                                const unsigned r = redux_add_u32(fx);
+                                if (lane == ((c0 + c) & 31)) mine = r;
+                            }
+                            so[2 * v] = pack_bf16x2(sv[0], sv[1]) & vmask;
+                            so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]) & vmask;
                         }
-                        st_global_v8(t_out + c0, lo);          // re-read right away by the softmax kernel: default policy
-                        st_global_v8(t_out + c0 + 8, hi);
+                        // columns c0 .. c0 + 15 went to lanes (c0 & 31) .. (c0 & 31) + 15
+                        if (static_cast<unsigned>(lane - (c0 & 31)) < 16u) {
+                            if (c0 < 32) keep_sum[0] += mine;
+                            else keep_sum[1] += mine;
+                        }
+                        __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
+                        const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
+                        st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
+                        st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
                     }
                 } else {
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
@@ -520,6 +582,19 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 // the warp for about a thousand cycles per tile.
                 if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * b);
             }
+            if constexpr (kFwd) {
+                // this warp's share of the query's row statistics: integer atomics, so the order in which the eight
+                // warps of the two CTAs arrive does not change the result
+#pragma unroll
+                for (int k = 0; k < NH / 32; ++k) {
+                    const int head = g * NH + 32 * k + lane;
+                    if (head < p.h_q) {
+                        const size_t o = static_cast<size_t>(qg) * p.h_q + head;
+                        if constexpr (kMode == 1) atomicMax(p.m_ord + o, keep_max[k]);
+                        else atomicAdd(p.l_fix + o, keep_sum[k]);
+                    }
+                }
+            }
         }
     }
     abort_wind_down(s_abort);
@@ -529,64 +604,12 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     if (warp == 16) tmem_dealloc_2cta(tmem, C::kTmemCols);
 }
 
-// =============================================================================================
-// forward softmax: one CTA per query, thread = (head, key slice).  Reads the base-2 logits the forward
-// recompute pass left in the scratch ([key][head] fp32, -inf where masked; 1 MB per query at h128 / top-k 2048,
-// so the second sweep hits L2), writes lse and the bf16 probabilities S = exp2(t - lse) for the o = S.V kernel.
-// A query without any valid slot gets lse = +inf and S = 0 (o = 0).
-// =============================================================================================
-template <int HP>
-__global__ void __launch_bounds__(512) smla_fwd_softmax_kernel(const KParams p) {
-    constexpr int kSlices = 512 / HP;
-    constexpr int kBatch = 8;                 // independent loads in flight per thread
-    const int ql = blockIdx.x;
-    const int qg = p.q0 + ql;
-    const int h = threadIdx.x % HP;
-    const int sl = threadIdx.x / HP;
-    const float* t_row = p.logits + static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + h;
-    __shared__ float m_s[512], l_s[512];
-    const float ninf = __int_as_float(0xff800000);
-    // sweep 1: max (topk_pad is a multiple of 256, so every thread sees whole batches)
-    float m = ninf;
-    for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
-        float t[kBatch];
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i) m = fmaxf(m, t[i]);
-    }
-    m_s[threadIdx.x] = m;
-    __syncthreads();
-    float mm = ninf;
-#pragma unroll
-    for (int i = 0; i < kSlices; ++i) mm = fmaxf(mm, m_s[i * HP + h]);
-    // sweep 2 (L2 hits): sum of exp2(t - max); exp2(-inf) = 0 takes care of masked slots
-    float l = 0.f;
-    if (mm != ninf) {
-        for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
-            float t[kBatch];
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i) l += ex2_approx(t[i] - mm);
-        }
-    }
-    l_s[threadIdx.x] = l;
-    __syncthreads();
-    float ll = 0.f;
-#pragma unroll
-    for (int i = 0; i < kSlices; ++i) ll += l_s[i * HP + h];
-    const float lse2 = (mm == ninf) ? __int_as_float(0x7f800000) : mm + __log2f(ll);
-    if (sl == 0 && h < p.h_q) p.lse_out[static_cast<size_t>(qg) * p.h_q + h] = lse2 * p.lse_out_mult;
-    // sweep 3: probabilities
-    __nv_bfloat16* s_q = p.s_scr + static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP;   // head-block-major layout, see scratch_offset
-    for (int key = sl; key < p.topk_pad; key += kSlices * kBatch) {
-        float t[kBatch];
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i) t[i] = t_row[static_cast<size_t>(key + i * kSlices) * HP];
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i)
-            s_q[scratch_offset(key + i * kSlices, h, p.topk_pad)] = __float2bfloat16_rn(ex2_approx(t[i] - lse2));
+// Row statistics of the forward start at -inf (maximum) and 0 (sum).
+__global__ void smla_fwd_stats_init_kernel(int* m_ord, unsigned long long* l_fix, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        m_ord[i] = kOrderedNegInf;
+        l_fix[i] = 0ull;
     }
 }
 
@@ -905,7 +928,7 @@ namespace dq {
 constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
-constexpr int kStages = 3;
+constexpr int kStages = 4;                // 4 x 56 KB: what is in flight bounds this kernel (3 stages: 4 % slower)
 template <int HP> struct Cfg {
     static constexpr int kKgBytes = 5 * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
@@ -913,11 +936,14 @@ template <int HP> struct Cfg {
     static constexpr int kOffMisc = kStages * kStage;
     // the A operand always spans 128 heads: with HP = 64 its upper half reads 8 KB past the dS tile
     static constexpr int kSmemBytes = kOffMisc + 256 + 1024 + (HP == 64 ? 8192 : 0);
+    static_assert(kSmemBytes <= 232448, "shared memory of one SM");
     static constexpr int kTmemCols = 512;                  // up to 320 columns of d used
 };
 }  // namespace dq
 
-template <int HP, int kSplit, int kTotal>
+// kNorm (forward, o = S.V): the scratch holds unnormalised E = exp2(logit - max); every head's row is divided by its
+// row sum on the way out, and the CTA of d-part 0 writes lse = max + log2(sum).
+template <int HP, int kSplit, int kTotal, bool kNorm = false>
 __global__ void __launch_bounds__(dq::kThreads, 1)
 smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
@@ -1056,6 +1082,17 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         constexpr int kRowBytes = 5 * 128 + 16;  // up to five column chunks per part
         const int head = quarter * 32 + lane;
         const uint32_t row_s = s_base + head * kRowBytes;
+        float inv = 1.f;
+        if constexpr (kNorm) {
+            if (head < p.h_q) {
+                const size_t o = static_cast<size_t>(qg) * p.h_q + head;
+                const float l = static_cast<float>(p.l_fix[o]) * (1.f / kFixScale);
+                inv = l > 0.f ? 1.f / l : 0.f;               // no valid slot: o = 0, lse = +inf
+                if (part == 0)
+                    p.lse_out[o] = (l > 0.f ? fmaf(ordered_to_float(p.m_ord[o]), p.scale_log2e, __log2f(l))
+                                            : __int_as_float(0x7f800000)) * p.lse_out_mult;
+            }
+        }
         if (quarter * 32 < p.h_q) {               // warp-uniform: heads are padded to a multiple of 8 only
             const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
@@ -1063,6 +1100,10 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + cg * 32, r);
                 tmem_ld_wait();
+                if constexpr (kNorm) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * inv);
+                }
 #pragma unroll
                 for (int v = 0; v < 4; ++v)
                     st_shared_v4(row_s + cg * 64 + v * 16,

@@ -288,3 +288,33 @@ def test_back_to_back_runs_repeat_bit_for_bit():
     assert op.device_status(ws) == 0
     ref = sparse_mla_bwd_ref(q, kv, dO, lse, O, idx, q_start_index_s=None, chunk_s=16)
     _assert_close(dq, dkv, ref[0].cpu(), ref[1].cpu())
+
+
+@pytest.mark.parametrize("h_q,topk,s_kv", [(128, 256, 300), (64, 96, 128), (16, 40, 64)])
+def test_all_ones_known_answers(h_q, topk, s_kv):
+    """All-ones inputs have exact integer answers, so a contraction that loses a K-step, a head or a key shows as a
+    wrong integer (the reference pins its sub-steps the same way: `ds_unit_tests/ds_tmem/test_ds_tmem.py:61-66`,
+    `ds_unit_tests/dkv_mma/test_dkv_mma.py:74-80`, `ds_unit_tests/dq_mma/test_dq_mma.py:69-74`).
+    q = kv = dO = 1, O = 1/2, sm_scale = 1/16, lse = 576/16 (natural log):  P = 576, S = 1, dP = 512, Delta = 256,
+    dS = (512 - 256)/16 = 16;  dQ = 16 x (valid slots of the query) in every element;  a dKV row touched by c slots holds
+    c * h_q * 17 in its first 512 columns (S.dO + dS.Q) and c * h_q * 16 in the last 64 (dS.Q only)."""
+    op = _op()
+    s_q = 7
+    g = torch.Generator().manual_seed(h_q + topk)
+    idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).to(torch.int32)
+    idx[torch.rand(s_q, topk, generator=g) < 0.25] = -1
+    idx[3] = s_kv            # a query with no valid slot at all
+    ones = lambda *shape: torch.ones(*shape, dtype=torch.bfloat16, device=DEV)
+    q, kv, dO = ones(s_q, h_q, 576), ones(s_kv, 576), ones(s_q, h_q, 512)
+    O = torch.full((s_q, h_q, 512), 0.5, dtype=torch.bfloat16, device=DEV)
+    lse = torch.full((s_q, h_q), 576.0 / 16.0, dtype=torch.float32, device=DEV)
+    dq, dkv = op.mla_bwd(q, kv, dO, lse, O, idx.to(DEV), sm_scale=1.0 / 16.0, q_start_index_s=None, lse_is_base2=False,
+                         check_device_status=True)
+    valid = (idx >= 0) & (idx < s_kv)
+    n_valid = valid.sum(1)
+    want_dq = (16.0 * n_valid).view(s_q, 1, 1).expand(s_q, h_q, 576)
+    assert torch.equal(dq.float().cpu(), want_dq.float())
+    count = torch.zeros(s_kv)
+    count.index_add_(0, idx[valid].long(), torch.ones(int(valid.sum())))
+    want_dkv = torch.cat([(count * h_q * 17.0).view(-1, 1).expand(s_kv, 512), (count * h_q * 16.0).view(-1, 1).expand(s_kv, 64)], 1)
+    assert torch.equal(dkv.cpu(), want_dkv)
