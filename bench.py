@@ -133,17 +133,13 @@ def _dist_setup(n_gpus: int):
     return rank, world, local
 
 
-def _config(wname, w, s_q, stages=None, sharding="none", schedule=None):
-    """The same keys for our arm and the reference arm."""
-    cfg = {"workload": wname, "batch": w.batch, "s_q": s_q or w.s_q, "s_kv": w.s_kv, "h_q": w.h_q, "topk": w.topk,
-           "d_qk": 576, "d_v": 512, "flops_per_slot": 5504, "q_start_index_s": w.q_start_index_s,
-           "lse": "base 2, from the fp32 forward", "sharding": sharding,
-           "l2": "inputs larger than L2 (no flush)"}
-    if stages is not None:
-        cfg["stages"] = stages
-    if schedule is not None:
-        cfg["schedule"] = {"chunks": schedule[0], "dkv_pairs": schedule[1]}
-    return cfg
+def _config(wname, w, s_q, sharding="none"):
+    """The workload: the same keys and values for our arm and the reference arm (what is particular to an arm - kernel
+    stages, schedule, the sample the CPU arm times - sits beside `config`, not in it)."""
+    return {"workload": wname, "batch": w.batch, "s_q": s_q or w.s_q, "s_kv": w.s_kv, "h_q": w.h_q, "topk": w.topk,
+            "d_qk": 576, "d_v": 512, "flops_per_slot": 5504, "q_start_index_s": w.q_start_index_s,
+            "lse": "base 2, from the fp32 forward", "sharding": sharding,
+            "l2": "inputs larger than L2 (no flush)"}
 
 
 def _oracle_run(seq, w, n_queries: int, threads: int):
@@ -667,9 +663,9 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": _config(wname, w, args.s_q, stages,
-                              ("query+reduce_scatter" if query_sharded else "batch") if world > 1 else "none",
-                              op.get_schedule()),
+            "config": _config(wname, w, args.s_q,
+                              ("query+reduce_scatter" if query_sharded else "batch") if world > 1 else "none"),
+            "stages": stages, "schedule": dict(zip(("chunks", "dkv_pairs"), op.get_schedule())),
             "clocks": clocks, "gpu_launches": n_launch, "kernels": kernels,
             "device_status": "ok" if not bad_status else "TIMEOUT in: " + "; ".join(bad_status),
         }
