@@ -126,8 +126,6 @@ def _dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # the pull-reduce reads peers with plain loads only; no multicast object is bound to its buffers
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return rank, world, local
@@ -293,6 +291,22 @@ def _query_sharded_block(op, sharding, dist, rank, world, dev, steps, warmup):
         pull = {"ms_per_step": ms_pull, "value": 5504.0 * w.s_q * w.h_q * w.topk / (ms_pull * 1e-3) / 1e12,
                 "collective_ms": ms_pull_coll, "max_abs_vs_nccl": d[0].item(), "max_ref": d[1].item(),
                 "how": "smla_dkv_pull_reduce between two symmetric-memory barriers; plain peer loads, sources cleared in the same kernel"}
+        # the same through the NVSwitch's in-network reduction, where the buffers have a multicast mapping
+        if reducer.multicast_ptr:
+            reducer.multimem = True
+            _, rows_mm = pull_step()
+            torch.cuda.synchronize()
+            dm = torch.tensor([(rows_mm - rows_nccl).abs().max().item()], dtype=torch.float64, device=dev)
+            dist.all_reduce(dm, op=dist.ReduceOp.MAX)
+            for _ in range(2):
+                pull_step()
+            ms_mm = timed(pull_step, steps)
+            ms_mm_coll = timed(lambda: reducer.reduce(out_rows), 10)
+            pull["multimem"] = {"ms_per_step": ms_mm, "value": 5504.0 * w.s_q * w.h_q * w.topk / (ms_mm * 1e-3) / 1e12,
+                                "collective_ms": ms_mm_coll, "max_abs_vs_nccl": dm[0].item(),
+                                "how": "smla_dkv_multimem_reduce: multimem.ld_reduce on the multicast mapping, multimem.st clears the sources"}
+        else:
+            pull["multimem"] = {"unavailable": "the symmetric memory has no multicast mapping on this box"}
         del reducer
     status = torch.tensor([op.device_status(ws)], dtype=torch.int64, device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)

@@ -79,6 +79,28 @@ int smla_bwd_run(const smla_bwd_params* p, void* workspace, size_t workspace_byt
 int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream,
                         int stage_mask);
 
+/* Whole backward with a REPRODUCIBLE dKV: the same inputs give the same bits in every run.  (No counterpart in the
+ * reference, whose scatter is an order-dependent reduce-add as well: mla_bwd/mla_bwd.cu:23-26,527-537.)
+ * The regular entry points add every slot's contribution into dKV with fp32 reductions, whose order - and so the
+ * rounding of a row's sum - differs from run to run (dQ is reproducible either way).  Here the dKV kernel writes every
+ * slot's [576] fp32 contribution to the slot's own row of `staging`, and a second kernel walks the index inverse of the
+ * sparse pattern (smla_index_inverse: CSR by kv row, flat slot ids ascending) and adds a kv row's slots in that order.
+ * Costs one extra write and read of 2304 bytes per slot (about 39 GB on the 4096-query x top-k 2048 workload).
+ *   row_ptr / entries: what smla_index_inverse returned for the same indices, s_kv and q_start_index_s;
+ *   staging: device memory, 16-byte aligned; a pass over the queries holds staging_bytes /
+ *            smla_bwd_staging_bytes_per_query(p) queries (at least one must fit), so a small buffer means more passes;
+ *   stage_mask as in smla_bwd_run_stages; without SMLA_STAGE_ZERO the sums are added to what dKV holds.
+ * query_meta must be null (one sequence).  Runs the kernels one after the other on `stream`. */
+typedef struct smla_bwd_det_params {
+    const int32_t* row_ptr; /* [s_kv + 1] */
+    const int32_t* entries; /* [s_q * topk] */
+    float* staging;
+    size_t staging_bytes;
+} smla_bwd_det_params;
+int smla_bwd_run_deterministic(const smla_bwd_params* p, const smla_bwd_det_params* det, void* workspace,
+                               size_t workspace_bytes, void* stream, int stage_mask);
+size_t smla_bwd_staging_bytes_per_query(const smla_bwd_params* p);
+
 /* Whole backward for callers that must not allocate device memory.  (No counterpart in the reference, whose
  * operator allocates delta, dQ and dKV itself on every call.)
  *
@@ -195,6 +217,13 @@ int smla_selftest_wait_timeout(void* workspace, int which, long long limit_cycle
  * ncclReduceScatter on this path. */
 int smla_dkv_pull_reduce(const void* const* partials, int32_t world, int32_t rank, int32_t s_kv, float* out,
                          int32_t zero_sources, void* stream);
+
+/* The same sum taken inside the NVSwitch, for buffers that also have a multicast (NVLS) mapping: `multicast_partial`
+ * is the multicast address of the partial buffers (what torch's symmetric memory calls multicast_ptr, offset to the
+ * buffer).  One multimem.ld_reduce returns the sum over all ranks, so a rank receives only its own reduced rows, and
+ * with zero_sources != 0 one multimem.st clears them in every rank's buffer.  Same barrier rules as above. */
+int smla_dkv_multimem_reduce(void* multicast_partial, int32_t world, int32_t rank, int32_t s_kv, float* out,
+                             int32_t zero_sources, void* stream);
 
 /* Measurement aid: every SM that gets a block writes {its cycle counter, the global nanosecond timer} to
  * out[2 * smid], out[2 * smid + 1] (device memory, 2 * n_sm x u64; SMs that got none keep what was there).  Two probes

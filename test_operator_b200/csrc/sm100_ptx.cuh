@@ -396,6 +396,15 @@ __device__ __forceinline__ void red_add_f32_if_row(float* addr, float v, int row
         : "memory");
 }
 
+// A plain store under the same predicate (the staged, reproducible form of the dKV scatter).
+__device__ __forceinline__ void st_global_f32_if_row(float* addr, float v, int row) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ge.s32 p, %2, 0;\n\t"
+        "@p st.global.f32 [%0], %1;\n\t}"
+        ::"l"(addr), "f"(v), "r"(row)
+        : "memory");
+}
 // The same with an L2 eviction policy: the accumulator rows are touched again by later queries and should
 // outlive the operands that only stream through.
 __device__ __forceinline__ void red_add_f32_if_row_hint(float* addr, float v, int row, uint64_t policy) {

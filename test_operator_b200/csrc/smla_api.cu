@@ -244,7 +244,8 @@ int resident_pairs(K kernel, int threads, int smem_bytes) {
 }
 
 template <int HP>
-int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages, bool allow_overlap) {
+int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStream_t st, int stages, bool allow_overlap,
+                 const smla_bwd_det_params* det = nullptr) {
     using namespace smla;
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
     __nv_bfloat16* ds_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.ds_off);
@@ -265,6 +266,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     // per device, so set on every call (cheap) rather than once per process
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, 0>, rp::Cfg<HP, 0>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_pair_kernel<HP>, dp::Cfg<HP>::kSmemBytes);
+    if (det) attr_ok &= set_smem(smla_dkv_pair_kernel<HP, true>, dp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dq_kernel<HP, kSplitChunk, kQChunks>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
@@ -292,6 +294,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 
     kp.qmeta = reinterpret_cast<const int4*>(p->query_meta);
     kp.wait_limit = g_wait_limit.load();
+    kp.staging = det ? det->staging : nullptr;
 
     if (stages & SMLA_STAGE_DELTA) {
         const int n_rows = p->s_q * p->h_q;
@@ -307,7 +310,17 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
         ++g_last_launches;
     };
     auto launch_dkv = [&](cudaStream_t s_, int pairs) {
-        smla_dkv_pair_kernel<HP><<<2 * (kp.nq < pairs ? kp.nq : pairs), dp::kThreads, dp::Cfg<HP>::kSmemBytes, s_>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
+        const int grid = 2 * (kp.nq < pairs ? kp.nq : pairs);
+        if (det) {
+            // reproducible form: per-slot contributions to the staging rows, then one warp per kv row adds its slots
+            // of this pass in CSR order
+            smla_dkv_pair_kernel<HP, true><<<grid, dp::kThreads, dp::Cfg<HP>::kSmemBytes, s_>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
+            smla_dkv_segment_sum_kernel<<<(p->s_kv + 7) / 8, 256, 0, s_>>>(det->row_ptr, det->entries, det->staging, p->dKV, p->s_kv,
+                                                                           p->topk, pl.topk_pad, kp.q0, kp.q0 + kp.nq);
+            g_last_launches += 2;
+            return;
+        }
+        smla_dkv_pair_kernel<HP><<<grid, dp::kThreads, dp::Cfg<HP>::kSmemBytes, s_>>>(tm_qhp, tm_dohp, tm_s, tm_ds, kp);
         ++g_last_launches;
     };
     auto launch_dq = [&](cudaStream_t s_) {
@@ -319,7 +332,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     schedule(&chunks, &dkv_pairs);
     const int all = SMLA_STAGE_RECOMPUTE | SMLA_STAGE_DKV | SMLA_STAGE_DQ;
     if (dkv_pairs <= 0) dkv_pairs = auto_dkv_pairs(HP, pairs_d < pairs_r ? pairs_d : pairs_r);
-    if (!allow_overlap || (stages & all) != all || dkv_pairs >= pairs_d || dkv_pairs >= pairs_r) chunks = 0;
+    if (!allow_overlap || det || (stages & all) != all || dkv_pairs >= pairs_d || dkv_pairs >= pairs_r) chunks = 0;
 
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
@@ -527,7 +540,7 @@ int smla_bwd_get_workspace_layout(const smla_bwd_params* p, size_t workspace_byt
 
 namespace {
 int run_stages_impl(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream, int stage_mask,
-                    bool allow_overlap) {
+                    bool allow_overlap, const smla_bwd_det_params* det = nullptr) {
     g_last_launches = 0;
     if (!check_params(p) || !workspace) return SMLA_ERR_BAD_ARG;
     if (!p->q || !p->kv || !p->dO || !p->lse || !p->O || !p->indices || !p->dQ || !p->dKV) return SMLA_ERR_BAD_ARG;
@@ -537,16 +550,36 @@ int run_stages_impl(const smla_bwd_params* p, void* workspace, size_t workspace_
         return SMLA_ERR_BAD_ARG;
     Plan pl;
     if (!plan_for_workspace(p, workspace_bytes, &pl)) return SMLA_ERR_WORKSPACE;
+    if (det) {
+        // a pass may hold no more queries than the staging buffer has rows for
+        if (p->query_meta || !det->row_ptr || !det->entries || !det->staging || !aligned16(det->staging)) return SMLA_ERR_BAD_ARG;
+        const size_t per_q = size_t(pl.topk_pad) * SMLA_D_QK * sizeof(float);
+        const size_t fit = det->staging_bytes / per_q;
+        if (fit < 1) return SMLA_ERR_WORKSPACE;
+        if (size_t(pl.q_chunk) > fit) pl.q_chunk = int(fit);
+    }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     if (stage_mask & SMLA_STAGE_ZERO) {
         if (cudaMemsetAsync(p->dKV, 0, size_t(p->s_kv) * SMLA_D_QK * sizeof(float), st) != cudaSuccess)
             return SMLA_ERR_LAUNCH;
     }
-    return pl.h_pad == 64 ? launch_chain<64>(p, pl, ws, st, stage_mask, allow_overlap)
-                          : launch_chain<128>(p, pl, ws, st, stage_mask, allow_overlap);
+    return pl.h_pad == 64 ? launch_chain<64>(p, pl, ws, st, stage_mask, allow_overlap, det)
+                          : launch_chain<128>(p, pl, ws, st, stage_mask, allow_overlap, det);
 }
 }  // namespace
+
+int smla_bwd_run_deterministic(const smla_bwd_params* p, const smla_bwd_det_params* det, void* workspace,
+                               size_t workspace_bytes, void* stream, int stage_mask) {
+    if (!det) return SMLA_ERR_BAD_ARG;
+    return run_stages_impl(p, workspace, workspace_bytes, stream, stage_mask, false, det);
+}
+
+size_t smla_bwd_staging_bytes_per_query(const smla_bwd_params* p) {
+    Plan pl;
+    if (!make_plan(p, 0, &pl)) return 0;
+    return size_t(pl.topk_pad) * SMLA_D_QK * sizeof(float);
+}
 
 int smla_bwd_run_stages(const smla_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream, int stage_mask) {
     return run_stages_impl(p, workspace, workspace_bytes, stream, stage_mask, true);
@@ -768,7 +801,45 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs peers, int wo
         }
     }
 }
+// The same sum taken inside the NVSwitch: one multimem.ld_reduce on the multicast mapping of the partial buffers
+// returns the sum over all ranks of 16 bytes, so a rank receives only its reduced rows (1/R of what the pull form
+// moves), and one multimem.st clears those 16 bytes in every rank's buffer at once.
+__global__ void __launch_bounds__(256) multimem_reduce_kernel(float4* __restrict__ mc, float4* __restrict__ out, size_t n4,
+                                                              size_t first4, int zero_sources) {
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 v;
+        float4* a = mc + first4 + i;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "l"(a)
+                     : "memory");
+        out[i] = v;
+        if (zero_sources)
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(0.f), "f"(0.f), "f"(0.f),
+                         "f"(0.f)
+                         : "memory");
+    }
+}
 }  // namespace
+
+int smla_dkv_multimem_reduce(void* multicast_partial, int32_t world, int32_t rank, int32_t s_kv, float* out,
+                             int32_t zero_sources, void* stream) {
+    if (!multicast_partial || !out || world < 1 || rank < 0 || rank >= world || s_kv <= 0 || s_kv % world) return SMLA_ERR_BAD_ARG;
+    if (!aligned16(multicast_partial) || !aligned16(out)) return SMLA_ERR_BAD_ARG;
+    const size_t rows = static_cast<size_t>(s_kv) / world;
+    const size_t n4 = rows * (SMLA_D_QK / 4);
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return SMLA_ERR_LAUNCH;
+    size_t blocks = (n4 + 255) / 256;
+    const size_t cap = static_cast<size_t>(sms) * 8;
+    if (blocks > cap) blocks = cap;
+    multimem_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<float4*>(multicast_partial), reinterpret_cast<float4*>(out), n4, static_cast<size_t>(rank) * n4, zero_sources);
+    g_last_launches = 1;
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
 
 int smla_dkv_pull_reduce(const void* const* partials, int32_t world, int32_t rank, int32_t s_kv, float* out,
                          int32_t zero_sources, void* stream) {

@@ -42,6 +42,7 @@ struct KParams {
     __nv_bfloat16* s_scr;     // [q_chunk][HP/8 head blocks][topk_pad keys][8 heads], see scratch_offset
     __nv_bfloat16* ds_scr;    // likewise
     float* dKV;               // [s_kv, 576]
+    float* staging;           // reproducible mode: [q_chunk][topk_pad slots][576] fp32, one row per slot
     __nv_bfloat16* dQ;        // [s_q, h_q, 576]
     // forward only
     int* m_ord;               // [s_q, h_q] row maximum of the raw logits Q.K, as order-preserving integers
@@ -653,7 +654,10 @@ template <int HP> struct Cfg {
 };
 }  // namespace dp
 
-template <int HP>
+// kStaged: instead of adding a slot's [576] contribution into dKV with fp32 reductions (whose order, and therefore
+// rounding, changes from run to run), write it to the slot's own row of a staging buffer; smla_dkv_segment_sum_kernel
+// then adds the rows that belong to one kv row in a fixed order.
+template <int HP, bool kStaged = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dp::kThreads, 1)
 smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
@@ -876,6 +880,11 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (mine) {
                     const int d0 = blk < 2 ? 256 * blk + 128 * static_cast<int>(rank) : 512 - 64;
                     float* out = p.dKV + d0 + quarter * 32 + lane;
+                    // staged form: the row of slot (query, first key of this warp's 64) in the staging buffer
+                    float* sout = nullptr;
+                    if constexpr (kStaged)
+                        sout = p.staging + (static_cast<size_t>(p.scr0 + ql) * p.topk_pad + tile * kTileKeys + 64 * e) * kDQK +
+                               d0 + quarter * 32 + lane;
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + us * 128 + 64 * e;
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
@@ -888,6 +897,11 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             ix[4 * v] = t.x; ix[4 * v + 1] = t.y; ix[4 * v + 2] = t.z; ix[4 * v + 3] = t.w;
                         }
                         tmem_ld_wait();
+                        if constexpr (kStaged) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                st_global_f32_if_row(sout + static_cast<size_t>(32 * i + j) * kDQK, __uint_as_float(r[j]), ix[j]);
+                        } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
 #ifdef SMLA_RED_EVICT_LAST
@@ -897,6 +911,7 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             red_add_f32_if_row(out + static_cast<size_t>(static_cast<unsigned>(ix[j])) * kDQK,
                                                __uint_as_float(r[j]), ix[j]);
 #endif
+                        }
                     }
                 }
                 // the accumulator reads have completed (tcgen05.wait::ld), which is all the issuer needs to know
@@ -913,6 +928,63 @@ smla_dkv_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (warp == 1) tmem_dealloc_2cta(tmem, 512);
 }
 
+
+// =============================================================================================
+// Reproducible dKV, second half: one warp per kv row walks the row's slots in the index inverse (CSR by kv row, flat
+// slot ids ascending) and adds their staged [576] contributions in that order, so a row's sum is rounded the same way
+// in every run.  A pass covers the queries [q_lo, q_hi); a row's slots of that range are a contiguous piece of its
+// CSR segment (found by binary search), and passes follow one another in a fixed order.
+// =============================================================================================
+__global__ void __launch_bounds__(256) smla_dkv_segment_sum_kernel(const int* __restrict__ row_ptr,
+                                                                   const int* __restrict__ entries,
+                                                                   const float* __restrict__ staging, float* __restrict__ dKV,
+                                                                   int s_kv, int topk, int topk_pad, int q_lo, int q_hi) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= s_kv) return;
+    const int b = __ldg(row_ptr + row), e = __ldg(row_ptr + row + 1);
+    auto lower = [&](long long flat) {      // first position in [b, e) whose flat slot id is >= flat
+        int lo = b, hi = e;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (__ldg(entries + mid) < flat) lo = mid + 1;
+            else hi = mid;
+        }
+        return lo;
+    };
+    const int i0 = lower(static_cast<long long>(q_lo) * topk), i1 = lower(static_cast<long long>(q_hi) * topk);
+    if (i1 <= i0) return;
+    constexpr int kPer = kDQK / 32;          // 18 elements per lane
+    float acc[kPer];
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) acc[k] = 0.f;
+    auto src_of = [&](int i) {
+        const int flat = __ldg(entries + i);
+        const int q = flat / topk;
+        return staging + (static_cast<size_t>(q - q_lo) * topk_pad + (flat - q * topk)) * kDQK + lane;
+    };
+    int i = i0;
+    for (; i + 1 < i1; i += 2) {             // two slots in flight; the additions keep the slot order
+        const float* s0 = src_of(i);
+        const float* s1 = src_of(i + 1);
+        float v0[kPer], v1[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            v0[k] = __ldcs(s0 + 32 * k);
+            v1[k] = __ldcs(s1 + 32 * k);
+        }
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) acc[k] = (acc[k] + v0[k]) + v1[k];
+    }
+    if (i < i1) {
+        const float* s0 = src_of(i);
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) acc[k] += __ldcs(s0 + 32 * k);
+    }
+    float* out = dKV + static_cast<size_t>(row) * kDQK + lane;
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) out[32 * k] += acc[k];
+}
 
 // =============================================================================================
 // dq: one CTA per (query, d-part); same d split as dkv; 14 warps.

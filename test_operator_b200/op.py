@@ -47,6 +47,11 @@ class _FwdParams(ctypes.Structure):
     ]
 
 
+class _DetParams(ctypes.Structure):
+    _fields_ = [("row_ptr", ctypes.c_void_p), ("entries", ctypes.c_void_p), ("staging", ctypes.c_void_p),
+                ("staging_bytes", ctypes.c_size_t)]
+
+
 class WorkspaceLayout(ctypes.Structure):
     _fields_ = [
         ("err_offset", ctypes.c_size_t), ("delta_offset", ctypes.c_size_t), ("s_offset", ctypes.c_size_t),
@@ -130,9 +135,17 @@ def load_library() -> ctypes.CDLL:
         lib.smla_selftest_wait_timeout.restype = ctypes.c_int
         lib.smla_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p,
                                                    ctypes.c_void_p]
+        lib.smla_bwd_run_deterministic.restype = ctypes.c_int
+        lib.smla_bwd_run_deterministic.argtypes = [ctypes.POINTER(_Params), ctypes.POINTER(_DetParams), ctypes.c_void_p,
+                                                   ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int]
+        lib.smla_bwd_staging_bytes_per_query.restype = ctypes.c_size_t
+        lib.smla_bwd_staging_bytes_per_query.argtypes = [ctypes.POINTER(_Params)]
         lib.smla_dkv_pull_reduce.restype = ctypes.c_int
         lib.smla_dkv_pull_reduce.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                              ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+        lib.smla_dkv_multimem_reduce.restype = ctypes.c_int
+        lib.smla_dkv_multimem_reduce.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                                 ctypes.c_int32, ctypes.c_void_p]
         lib.smla_clock_probe.restype = ctypes.c_int
         lib.smla_clock_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.smla_bwd_status_string = lib.smla_status_string
@@ -187,10 +200,28 @@ def _cached_workspace(need: int, device: torch.device) -> Workspace:
         return ws
 
 
+_buf_cache = {}
+
+
+def _cached_buffer(kind: str, need: int, device: torch.device) -> torch.Tensor:
+    """A byte buffer kept per (kind, device, stream) and grown on demand, like the workspaces."""
+    key = (kind, device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    with _ws_cache_lock:
+        buf = _buf_cache.get(key)
+        if buf is None or buf.numel() < need:
+            _buf_cache.pop(key, None)
+            buf = None
+            buf = torch.empty(need, dtype=torch.uint8, device=device)
+            _buf_cache[key] = buf
+        return buf
+
+
 def release_cached_workspaces() -> None:
-    """Drop the workspaces kept for calls that pass none (they are re-created on demand)."""
+    """Drop the workspaces and staging buffers kept for calls that pass none (they are re-created on demand)."""
     with _ws_cache_lock:
         _ws_cache.clear()
+        _buf_cache.clear()
 
 
 def _make_params(q, kv2, dO, lse, O, idx2, dQ, dKV2, sm_scale, q_start_index_s, lse_is_base2,
@@ -264,6 +295,8 @@ def mla_bwd(
     check_device_status: bool = False,
     out_dq: Optional[torch.Tensor] = None,
     query_meta: Optional[torch.Tensor] = None,
+    deterministic: bool = False,
+    staging_budget: int = 2 << 30,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sparse MLA attention backward.  Returns (dQ bf16 [s_q,h_q,576], dKV fp32 shaped like kv).
 
@@ -274,8 +307,11 @@ def mla_bwd(
     `out_dq` receives dQ in place.  `query_meta` (int32 [s_q, 4] on the device: first kv row and number of
     kv rows of the query's sequence, position for the causal rule, top-k slots in use) lets one call cover
     packed sequences; see `query_meta_for`.  Without `workspace` the scratch comes from a cache kept per
-    (device, stream).  The call enqueues on the current stream and does not synchronise unless
-    `check_device_status=True`, which also raises if a kernel reported a timed-out wait.
+    (device, stream).  `deterministic=True` makes dKV reproducible bit for bit (dQ always is): the index inverse of the
+    sparse pattern is built (`index_inverse`), every slot's contribution goes to a staging buffer of at most about
+    `staging_budget` bytes and is added per kv row in a fixed order - slower (one extra write and read of 2304
+    bytes per slot), for runs that must repeat exactly.  The call enqueues on the current stream and does not
+    synchronise unless `check_device_status=True`, which also raises if a kernel reported a timed-out wait.
     """
     _validate(q, kv, dO, lse, O, indices)
     _check_query_meta(query_meta, q)
@@ -302,7 +338,19 @@ def mla_bwd(
             workspace = Workspace(need, q.device) if workspace_budget else _cached_workspace(need, q.device)
         stream = torch.cuda.current_stream().cuda_stream
         stages = STAGE_ALL & ~STAGE_ZERO if accumulate else STAGE_ALL
-        st = lib.smla_bwd_run_stages(ctypes.byref(params), workspace.ptr, workspace.nbytes, stream, stages)
+        if deterministic:
+            _check(query_meta is None, "deterministic=True handles one sequence per call (no query_meta)")
+            row_ptr, entries = index_inverse(idx2, kv2.shape[0], q_start_index_s)
+            per_q = lib.smla_bwd_staging_bytes_per_query(ctypes.byref(params))
+            n_stage = max(1, min(q.shape[0], max(int(staging_budget), per_q) // per_q))
+            staging = _cached_buffer("staging", n_stage * per_q, q.device)
+            det = _DetParams(row_ptr.data_ptr(), entries.data_ptr(), staging.data_ptr(), staging.numel())
+            st = lib.smla_bwd_run_deterministic(ctypes.byref(params), ctypes.byref(det), workspace.ptr, workspace.nbytes,
+                                                stream, stages)
+            for t in (row_ptr, entries):
+                t.record_stream(torch.cuda.current_stream())
+        else:
+            st = lib.smla_bwd_run_stages(ctypes.byref(params), workspace.ptr, workspace.nbytes, stream, stages)
         _raise_status(lib, st, "smla_bwd_run")
         if check_device_status:
             _raise_status(lib, lib.smla_bwd_status(workspace.ptr, stream), "smla_bwd device status")

@@ -65,9 +65,11 @@ class PullReducer:
     it starts at zero, and every `reduce()` leaves it at zero again (each rank clears the rows it has read, in every
     rank's buffer).  `reduce()` runs on the current stream between two cross-rank barriers of the symmetric-memory
     handle: every rank must call it once per step, like a collective.  torch provides the memory mapping and the
-    barriers; the reduction itself is this library's kernel, reading peers with plain loads (no TMA, no multicast)."""
+    barriers; the reduction itself is this library's kernel.  Two forms: plain peer loads (always available), and -
+    where the symmetric memory also has an NVSwitch multicast mapping and `multimem=True` - `multimem.ld_reduce`, which
+    lets the switch add the ranks' copies so that a rank receives only its reduced rows."""
 
-    def __init__(self, s_kv: int, device, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, s_kv: int, device, group: Optional[dist.ProcessGroup] = None, multimem: bool = False):
         import ctypes
         import torch.distributed._symmetric_memory as symm_mem
         from . import op
@@ -86,6 +88,9 @@ class PullReducer:
         if ptrs[self.rank] != self.partial.data_ptr():
             raise RuntimeError("symmetric memory handle does not describe the partial buffer")
         self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        mc = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc + offset if mc else 0
+        self.multimem = bool(multimem and self.multicast_ptr)
         self._lib = op.load_library()
         self._raise = op._raise_status
 
@@ -96,8 +101,11 @@ class PullReducer:
             out = torch.empty(n, self.partial.shape[1], dtype=torch.float32, device=self.partial.device)
         stream = torch.cuda.current_stream().cuda_stream
         self.hdl.barrier(channel=0)            # every rank's backward has finished writing its partial
-        self._raise(self._lib, self._lib.smla_dkv_pull_reduce(self._ptrs, self.world, self.rank, self.s_kv, out.data_ptr(), 1, stream),
-                    "smla_dkv_pull_reduce")
+        if self.multimem:
+            st = self._lib.smla_dkv_multimem_reduce(self.multicast_ptr, self.world, self.rank, self.s_kv, out.data_ptr(), 1, stream)
+        else:
+            st = self._lib.smla_dkv_pull_reduce(self._ptrs, self.world, self.rank, self.s_kv, out.data_ptr(), 1, stream)
+        self._raise(self._lib, st, "smla_dkv_pull_reduce")
         self.hdl.barrier(channel=1)            # every rank has finished reading (and clearing) before anyone writes again
         return out
 

@@ -36,6 +36,11 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
 
     dq_ref, dkv_ref = op.mla_bwd(t["q"], t["kv"], t["dO"], t["lse"], t["O"], t["indices"], q_start_index_s=None,
                                  check_device_status=True)
+    # the regular entry point is itself held to the oracle on this shape, so that "equal to it" means "right"
+    from oracle.sparse_mla_ref import sparse_mla_bwd_ref
+    from tests.metrics import assert_backward_close
+    assert_backward_close(dq_ref, dkv_ref, *sparse_mla_bwd_ref(t["q"], t["kv"], t["dO"], t["lse"], t["O"], t["indices"],
+                                                               q_start_index_s=None, chunk_s=16))
     for call in range(2):
         dq = torch.full_like(t["q"], float("nan"))
         dkv = torch.full(t["kv"].shape, float("nan"), dtype=torch.float32, device=DEV)
