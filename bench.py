@@ -280,33 +280,29 @@ def _query_sharded_block(op, sharding, dist, rank, world, dev, steps, warmup):
             return sharding.query_sharded_bwd(op.mla_bwd, mine["q"], kv, mine["dO"], mine["lse"], mine["O"], mine["indices"],
                                               r0, qs, reducer=reducer, workspace=ws)
         _, rows_nccl = step()
-        _, rows_pull = pull_step()
-        torch.cuda.synchronize()
-        d = torch.tensor([(rows_pull - rows_nccl).abs().max().item(), rows_nccl.abs().max().item()], dtype=torch.float64, device=dev)
-        dist.all_reduce(d, op=dist.ReduceOp.MAX)
-        for _ in range(2):
-            pull_step()
-        ms_pull = timed(pull_step, steps)
-        ms_pull_coll = timed(lambda: reducer.reduce(out_rows), 10)
-        pull = {"ms_per_step": ms_pull, "value": 5504.0 * w.s_q * w.h_q * w.topk / (ms_pull * 1e-3) / 1e12,
-                "collective_ms": ms_pull_coll, "max_abs_vs_nccl": d[0].item(), "max_ref": d[1].item(),
-                "how": "smla_dkv_pull_reduce between two symmetric-memory barriers; plain peer loads, sources cleared in the same kernel"}
-        # the same through the NVSwitch's in-network reduction, where the buffers have a multicast mapping
+        ref_max = rows_nccl.abs().max().item()
+        pull = {"max_ref": ref_max,
+                "how": "smla_dkv_pull_reduce (plain peer loads) / smla_dkv_multimem_reduce (multimem.ld_reduce through the NVSwitch) "
+                       "between two symmetric-memory barriers; fused_zero: the kernel also clears what it read in every rank's "
+                       "buffer, so the backward accumulates and runs no memset"}
+        variants = [("peer_loads", False, False), ("peer_loads_fused_zero", False, True)]
         if reducer.multicast_ptr:
-            reducer.multimem = True
-            _, rows_mm = pull_step()
-            torch.cuda.synchronize()
-            dm = torch.tensor([(rows_mm - rows_nccl).abs().max().item()], dtype=torch.float64, device=dev)
-            dist.all_reduce(dm, op=dist.ReduceOp.MAX)
-            for _ in range(2):
-                pull_step()
-            ms_mm = timed(pull_step, steps)
-            ms_mm_coll = timed(lambda: reducer.reduce(out_rows), 10)
-            pull["multimem"] = {"ms_per_step": ms_mm, "value": 5504.0 * w.s_q * w.h_q * w.topk / (ms_mm * 1e-3) / 1e12,
-                                "collective_ms": ms_mm_coll, "max_abs_vs_nccl": dm[0].item(),
-                                "how": "smla_dkv_multimem_reduce: multimem.ld_reduce on the multicast mapping, multimem.st clears the sources"}
+            variants += [("multimem", True, False), ("multimem_fused_zero", True, True)]
         else:
             pull["multimem"] = {"unavailable": "the symmetric memory has no multicast mapping on this box"}
+        for name, mm, fz in variants:
+            reducer.multimem, reducer.zero_sources = mm, fz
+            reducer.partial.zero_()
+            barrier()
+            _, rows_v = pull_step()
+            torch.cuda.synchronize()
+            d = torch.tensor([(rows_v - rows_nccl).abs().max().item()], dtype=torch.float64, device=dev)
+            dist.all_reduce(d, op=dist.ReduceOp.MAX)
+            pull_step()
+            ms_v = timed(pull_step, steps)
+            ms_v_coll = timed(lambda: reducer.reduce(out_rows), 10)
+            pull[name] = {"ms_per_step": ms_v, "value": 5504.0 * w.s_q * w.h_q * w.topk / (ms_v * 1e-3) / 1e12,
+                          "collective_ms": ms_v_coll, "max_abs_vs_nccl": d[0].item()}
         del reducer
     status = torch.tensor([op.device_status(ws)], dtype=torch.int64, device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)

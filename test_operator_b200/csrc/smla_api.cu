@@ -806,19 +806,30 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(PeerPtrs peers, int wo
 // moves), and one multimem.st clears those 16 bytes in every rank's buffer at once.
 __global__ void __launch_bounds__(256) multimem_reduce_kernel(float4* __restrict__ mc, float4* __restrict__ out, size_t n4,
                                                               size_t first4, int zero_sources) {
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        float4 v;
-        float4* a = mc + first4 + i;
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                     : "l"(a)
-                     : "memory");
-        out[i] = v;
-        if (zero_sources)
-            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(0.f), "f"(0.f), "f"(0.f),
-                         "f"(0.f)
-                         : "memory");
+    constexpr int kUnroll = 4;              // independent reductions in flight per thread
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n4; i0 += kUnroll * stride) {
+        float4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < n4)
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(v[u].x), "=f"(v[u].y), "=f"(v[u].z), "=f"(v[u].w)
+                             : "l"(mc + first4 + i)
+                             : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < n4) {
+                out[i] = v[u];
+                if (zero_sources)
+                    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc + first4 + i), "f"(0.f),
+                                 "f"(0.f), "f"(0.f), "f"(0.f)
+                                 : "memory");
+            }
+        }
     }
 }
 }  // namespace

@@ -61,15 +61,18 @@ class PullReducer:
     """The ranks' partial dKV buffers in symmetric memory (every rank's buffer mapped into every process of the node)
     and the pull-reduce kernel `smla_dkv_pull_reduce` in place of NCCL's reduce-scatter.
 
-    `partial` is this rank's [s_kv, 576] fp32 buffer: pass it to the operator as `out_dkv` with `accumulate=True` -
-    it starts at zero, and every `reduce()` leaves it at zero again (each rank clears the rows it has read, in every
-    rank's buffer).  `reduce()` runs on the current stream between two cross-rank barriers of the symmetric-memory
-    handle: every rank must call it once per step, like a collective.  torch provides the memory mapping and the
+    `partial` is this rank's [s_kv, 576] fp32 buffer: pass it to the operator as `out_dkv`.  With `zero_sources=True`
+    every `reduce()` leaves all partials at zero again (each rank clears the rows it has read, in every rank's buffer),
+    so the operator can run with `accumulate=True` and no memset; that saves a 151 MB local clear per step but sends as
+    many zeros over NVLink as data was read, which costs more than it saves from four ranks up (the links are the
+    bound) - hence off by default.  `reduce()` runs on the current stream between two cross-rank barriers of the
+    symmetric-memory handle: every rank must call it once per step, like a collective.  torch provides the memory mapping and the
     barriers; the reduction itself is this library's kernel.  Two forms: plain peer loads (always available), and -
     where the symmetric memory also has an NVSwitch multicast mapping and `multimem=True` - `multimem.ld_reduce`, which
     lets the switch add the ranks' copies so that a rank receives only its reduced rows."""
 
-    def __init__(self, s_kv: int, device, group: Optional[dist.ProcessGroup] = None, multimem: bool = False):
+    def __init__(self, s_kv: int, device, group: Optional[dist.ProcessGroup] = None, multimem: bool = False,
+                 zero_sources: bool = False):
         import ctypes
         import torch.distributed._symmetric_memory as symm_mem
         from . import op
@@ -91,20 +94,22 @@ class PullReducer:
         mc = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
         self.multicast_ptr = mc + offset if mc else 0
         self.multimem = bool(multimem and self.multicast_ptr)
+        self.zero_sources = bool(zero_sources)
         self._lib = op.load_library()
         self._raise = op._raise_status
 
     def reduce(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Sum of all ranks' partials over this rank's rows [s_kv / R, 576]; clears the partials."""
+        """Sum of all ranks' partials over this rank's rows [s_kv / R, 576] (and, with `zero_sources`, clear them)."""
         n = self.rows[1] - self.rows[0]
         if out is None:
             out = torch.empty(n, self.partial.shape[1], dtype=torch.float32, device=self.partial.device)
         stream = torch.cuda.current_stream().cuda_stream
         self.hdl.barrier(channel=0)            # every rank's backward has finished writing its partial
+        z = 1 if self.zero_sources else 0
         if self.multimem:
-            st = self._lib.smla_dkv_multimem_reduce(self.multicast_ptr, self.world, self.rank, self.s_kv, out.data_ptr(), 1, stream)
+            st = self._lib.smla_dkv_multimem_reduce(self.multicast_ptr, self.world, self.rank, self.s_kv, out.data_ptr(), z, stream)
         else:
-            st = self._lib.smla_dkv_pull_reduce(self._ptrs, self.world, self.rank, self.s_kv, out.data_ptr(), 1, stream)
+            st = self._lib.smla_dkv_pull_reduce(self._ptrs, self.world, self.rank, self.s_kv, out.data_ptr(), z, stream)
         self._raise(self._lib, st, "smla_dkv_pull_reduce")
         self.hdl.barrier(channel=1)            # every rank has finished reading (and clearing) before anyone writes again
         return out
@@ -122,8 +127,9 @@ def query_sharded_bwd(bwd_fn, q_blk, kv, dO_blk, lse_blk, O_blk, idx_blk, q_row0
     """
     qs = None if q_start_index_s is None else q_start_index_s + q_row0
     if reducer is not None:
+        # partials the previous reduce() left clear are accumulated into; otherwise the operator clears them first
         dq, _ = bwd_fn(q_blk, kv, dO_blk, lse_blk, O_blk, idx_blk, q_start_index_s=qs, out_dkv=reducer.partial,
-                       accumulate=True, **kw)
+                       accumulate=reducer.zero_sources, **kw)
         return dq, reducer.reduce()
     if partial is None:
         partial = torch.empty(kv.shape, dtype=torch.float32, device=kv.device)

@@ -40,8 +40,10 @@ def _worker(rank, world, port, ret):
             r0, r1 = sharding.query_block(w.s_q, rank, world)
             k0, k1 = sharding.kv_rows_of_rank(w.s_kv, rank, world)
             blk = [s[k][r0:r1].contiguous() for k in keys]
-            reducer = sharding.PullReducer(w.s_kv, dev)
-            for name, kw in (("nccl", {}), ("pull", {"reducer": reducer}), ("pull again", {"reducer": reducer})):
+            reducer = sharding.PullReducer(w.s_kv, dev, zero_sources=True)
+            plain = sharding.PullReducer(w.s_kv, dev)       # partials cleared by the operator, not by the reduction
+            for name, kw in (("nccl", {}), ("pull", {"reducer": reducer}), ("pull again", {"reducer": reducer}),
+                             ("plain pull", {"reducer": plain}), ("plain pull again", {"reducer": plain})):
                 dq, rows = sharding.query_sharded_bwd(op.mla_bwd, blk[0], s["kv"], blk[1], blk[2], blk[3], blk[4], r0, q_start,
                                                       check_device_status=True, **kw)
                 torch.cuda.synchronize()
@@ -49,11 +51,11 @@ def _worker(rank, world, port, ret):
                 fk = error_figures(dkv_ref[k0:k1], rows)
                 assert fq["rel_diff"] < 0.01 and fq["cosine"] > 0.99999 and fq["max_abs"] <= 2 ** -7 * fq["max_ref"] + 1e-6, (name, fq)
                 assert fk["rel_diff"] < 0.01 and fk["cosine"] > 0.99999 and fk["max_abs"] <= 2 ** -8 * fk["max_ref"] + 1e-6, (name, fk)
-                if name.startswith("pull"):
+                if name.startswith("pull"):   # the fused-zero form
                     dist.barrier()
                     torch.cuda.synchronize()
                     assert torch.count_nonzero(reducer.partial).item() == 0, "the pull-reduce leaves every partial clear"
-            del reducer
+            del reducer, plain
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
