@@ -363,10 +363,10 @@ __device__ __forceinline__ void st_global_v8(void* addr, const uint32_t (&v)[8])
 }
 
 // ---- small helpers -----------------------------------------------------------------------------
-// Integer reductions over the 32 lanes of a warp in one instruction (every lane receives the result).
-__device__ __forceinline__ int redux_max_s32(int v) {
-    int r;
-    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+// Reductions over the 32 lanes of a warp in one instruction (every lane receives the result).
+__device__ __forceinline__ float redux_max_f32(float v) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
     return r;
 }
 __device__ __forceinline__ unsigned redux_add_u32(unsigned v) {

@@ -461,7 +461,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 stat_next = load_stat(ql + n_pairs);
             }
             // forward: what this lane keeps for heads g * NH + lane and g * NH + 32 + lane over the query's tiles
-            int keep_max[2] = {kOrderedNegInf, kOrderedNegInf};
+            float keep_max[2] = {__int_as_float(0xff800000), __int_as_float(0xff800000)};
             unsigned long long keep_sum[2] = {0ull, 0ull};
             for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
                 const int key = tile * kTileKeys + rank * 128 + row;
@@ -480,14 +480,14 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         uint32_t pv[32];
                         tmem_ld_32x32(taddr + c0, pv);
                         tmem_ld_wait();
-                        int mine = kOrderedNegInf;
+                        float mine = ninf;
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
-                            const int r = redux_max_s32(float_to_ordered(valid ? __uint_as_float(pv[c]) : ninf));
+                            const float r = redux_max_f32(valid ? __uint_as_float(pv[c]) : ninf);
                             if (lane == c) mine = r;
                         }
-                        if (c0 == 0) keep_max[0] = max(keep_max[0], mine);
-                        else keep_max[1] = max(keep_max[1], mine);
+                        if (c0 == 0) keep_max[0] = fmaxf(keep_max[0], mine);
+                        else keep_max[1] = fmaxf(keep_max[1], mine);
                     }
                 } else if constexpr (kMode == 2) {
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
@@ -539,12 +539,8 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     __nv_bfloat16* s_out = p.s_scr + off;
                     __nv_bfloat16* ds_out = p.ds_scr + off;
                     const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < NH; c0 += 16) {
-                        uint32_t pv[16], dpv[16];
-                        tmem_ld_32x16(taddr + c0, pv);
-                        tmem_ld_32x16(taddr + NH + c0, dpv);
-                        tmem_ld_wait();
+                    // 16 heads at a time (loading the next 16 columns under the work on these was measured: no change)
+                    auto work = [&](int c0, const uint32_t (&pv)[16], const uint32_t (&dpv)[16]) {
                         uint32_t so[8], dso[8];
                         const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);     // 16 heads: 4 + 4 vector loads
                         const float4* d4 = reinterpret_cast<const float4*>(delta_s + g * NH + c0);
@@ -568,16 +564,22 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                             dso[2 * v] = pack_bf16x2(dsv[0], dsv[1]) & vmask;
                             dso[2 * v + 1] = pack_bf16x2(dsv[2], dsv[3]) & vmask;
                         }
-                        {
-                            // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
-                            __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
-                            __nv_bfloat16* d0 = ds_out + static_cast<size_t>(c0) * p.topk_pad;
-                            const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
-                            st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
-                            st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
-                            st_global_v4_hint(d0, dso[0], dso[1], dso[2], dso[3], pol_stream);
-                            st_global_v4_hint(d0 + blk, dso[4], dso[5], dso[6], dso[7], pol_stream);
-                        }
+                        // 16 heads = two blocks of 8; a block is topk_pad * 8 elements further
+                        __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
+                        __nv_bfloat16* d0 = ds_out + static_cast<size_t>(c0) * p.topk_pad;
+                        const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
+                        st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
+                        st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
+                        st_global_v4_hint(d0, dso[0], dso[1], dso[2], dso[3], pol_stream);
+                        st_global_v4_hint(d0 + blk, dso[4], dso[5], dso[6], dso[7], pol_stream);
+                    };
+#pragma unroll 1
+                    for (int c0 = 0; c0 < NH; c0 += 16) {
+                        uint32_t pv[16], dpv[16];
+                        tmem_ld_32x16(taddr + c0, pv);
+                        tmem_ld_32x16(taddr + NH + c0, dpv);
+                        tmem_ld_wait();
+                        work(c0, pv, dpv);
                     }
                 }
                 tc_fence_before_sync();
@@ -595,7 +597,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     const int head = g * NH + 32 * k + lane;
                     if (head < p.h_q) {
                         const size_t o = static_cast<size_t>(qg) * p.h_q + head;
-                        if constexpr (kMode == 1) atomicMax(p.m_ord + o, keep_max[k]);
+                        if constexpr (kMode == 1) atomicMax(p.m_ord + o, float_to_ordered(keep_max[k]));
                         else atomicAdd(p.l_fix + o, keep_sum[k]);
                     }
                 }
