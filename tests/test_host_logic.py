@@ -49,6 +49,41 @@ def test_struct_layout_matches_header_field_order():
     assert fields == [f[0] for f in op._Params._fields_]
 
 
+def _header_fields(struct_name):
+    hdr = open(os.path.join(ROOT, "include", "smla_bwd.h")).read()
+    body = hdr[hdr.index("typedef struct %s {" % struct_name): hdr.index("} %s;" % struct_name)]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split("{", 1)[1].split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        for part in decl.split(","):
+            fields.append(re.findall(r"([A-Za-z_0-9]+)$", part.strip())[0])
+    return fields
+
+
+def test_other_struct_layouts_match_the_header():
+    assert _header_fields("smla_bwd_params") == [f[0] for f in op._Params._fields_]
+    assert _header_fields("smla_fwd_params") == [f[0] for f in op._FwdParams._fields_]
+    assert _header_fields("smla_bwd_det_params") == [f[0] for f in op._DetParams._fields_]
+    assert _header_fields("smla_bwd_workspace_layout") == [f[0] for f in op.WorkspaceLayout._fields_]
+
+
+def test_new_entry_points_refuse_bad_arguments_without_a_gpu():
+    lib = op.load_library()
+    p = op._Params(0, 0, 0, 0, 0, 0, 0, 0, 64, 256, 16, 64, 0.0, 0, 1)
+    assert lib.smla_bwd_staging_bytes_per_query(ctypes.byref(p)) == 256 * 576 * 4       # top-k padded to 256 slots
+    assert lib.smla_bwd_run_deterministic(ctypes.byref(p), None, None, 0, None, 31) == 1
+    assert lib.smla_bwd_set_schedule(1, 0) == 1 and lib.smla_bwd_set_schedule(-1, 0) == 1
+    c, d = op.get_schedule()
+    assert c == 2 and d == 0                                                         # the library's default
+    assert lib.smla_dkv_pull_reduce(None, 2, 0, 64, None, 0, None) == 1
+    assert lib.smla_dkv_multimem_reduce(None, 2, 0, 64, None, 0, None) == 1
+    assert lib.smla_selftest_wait_timeout(None, 0, 1000, None, None) == 1
+    assert lib.smla_bwd_workspace_init(None, None) == 1
+
+
 def test_workspace_size_and_bad_arguments_without_a_gpu():
     lib = op.load_library()
     p = op._Params(0, 0, 0, 0, 0, 0, 0, 0, 4096, 32768, 128, 2048, 0.0, 0, 1)
