@@ -67,3 +67,17 @@ def test_varlen_rejects_bad_offsets():
         op.mla_bwd_varlen(*dev, [0, 3], [0, 64])            # does not cover q
     with pytest.raises(RuntimeError):
         op.mla_bwd_varlen(*dev, [0, 4], [0, 32, 64])        # lengths differ
+
+
+def test_batched_large_enough_for_the_overlapped_schedule():
+    """1200 packed queries: the per-query table and the two-stream schedule together (the small cases above run the
+    kernels one after the other)."""
+    from test_operator_b200 import op
+    w = Workload("bl", 1, 400, 640, 128, 256, "uniform", invalid_frac=0.1)
+    seqs = [make_sequence(w, device=DEV, seed=61 + b) for b in range(3)]
+    stacked = {k: torch.stack([s[k] for s in seqs]) for k in KEYS}
+    dq, dkv = op.mla_bwd_batched(*[stacked[k] for k in KEYS], q_start_index_s=300, check_device_status=True)
+    assert op.last_launch_count() == 1 + 3 * max(1, op.get_schedule()[0])
+    for b, s in enumerate(seqs):
+        dq_ref, dkv_ref = sparse_mla_bwd_ref(*[s[k] for k in KEYS], q_start_index_s=300, chunk_s=16)
+        assert_backward_close(dq[b], dkv[b], dq_ref, dkv_ref, f"sequence {b}")
