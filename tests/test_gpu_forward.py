@@ -117,3 +117,30 @@ def test_forward_and_natural_log_backward_against_reference_phase_test_golden(na
     for mine, gold in ((S[rows, :64, :128].float(), S_gold), (dS[rows, :64, :128].float(), dS_gold)):
         err = (mine - gold).abs()
         assert torch.all(err <= 2 ** -7 * gold.abs() + 2e-4 * gold.abs().max())
+
+
+def test_forward_over_packed_sequences_with_a_query_table():
+    """Two sequences of different length packed along the first dimension, one forward call: the per-query table
+    tells the kernels which kv rows a query may touch, its causal position and how many of its slots are in use."""
+    from test_operator_b200 import op
+    shapes = [(7, 200), (12, 333)]
+    topk, h_q = 64, 64
+    seqs = [make_sequence(Workload("fv", 1, sq, skv, h_q, topk, "uniform", invalid_frac=0.1), device="cpu", seed=70 + i,
+                          with_forward=False) for i, (sq, skv) in enumerate(shapes)]
+    q = torch.cat([s["q"] for s in seqs]).to(DEV)
+    kv = torch.cat([s["kv"] for s in seqs]).to(DEV)
+    idx = torch.cat([s["indices"] for s in seqs]).to(DEV)
+    lens = torch.randint(1, topk + 1, (q.shape[0],), generator=torch.Generator().manual_seed(3), dtype=torch.int32)
+    meta = op.query_meta_for([0, 7], [7, 12], [0, 200], [200, 333], DEV, 150, topk, lens)
+    o, lse = op.mla_fwd(q, kv, idx, q_start_index_s=150, query_meta=meta, check_device_status=True)
+    r0 = 0
+    for s, (sq, skv) in zip(seqs, shapes):
+        ii = s["indices"].clone()
+        ii[torch.arange(topk)[None, :] >= lens[r0:r0 + sq, None].long()] = -1
+        o_ref, lse_ref = sparse_mla_fwd_ref(s["q"], s["kv"], ii, q_start_index_s=150)
+        fin = torch.isfinite(lse_ref)
+        got = lse[r0:r0 + sq].cpu()
+        assert torch.equal(torch.isinf(got), ~fin)
+        assert torch.allclose(got[fin], lse_ref[fin] * LOG2E, rtol=0, atol=2e-4)
+        assert cosine(o[r0:r0 + sq].float().cpu(), o_ref) > 0.9999
+        r0 += sq
