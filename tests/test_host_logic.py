@@ -194,3 +194,40 @@ def test_index_inverse_oracle_forms_agree_and_abi_rejects_bad_shapes():
     assert lib.smla_index_inverse_workspace_size(1 << 20, 1 << 12, 10) == 0      # s_q * topk needs more than 31 bits
     assert lib.smla_index_inverse(None, 4, 32, 0, 0, None, None, None, 0, None) == 1
     assert lib.smla_index_inverse(None, 4, 32, 10, 0, None, None, None, 0, None) == 1
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 and a C program links the library and calls it (entry
+    points that need no device: sizes, argument checks, the status text)."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    lib = op.load_library()
+    lib_dir = os.path.dirname(lib._name)
+    src = tmp_path / "abi.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "smla_bwd.h"
+int main(void) {
+    smla_bwd_params p;
+    memset(&p, 0, sizeof p);
+    p.s_q = 4096; p.s_kv = 32768; p.h_q = 128; p.topk = 2048; p.q_start_index_s = SMLA_NO_CAUSAL; p.lse_is_base2 = 1;
+    size_t need = smla_bwd_workspace_size(&p, 0);
+    if (need < (size_t)4096 * 2048 * 128 * 4) return 1;
+    if (smla_bwd_run(&p, NULL, 0, NULL) != SMLA_ERR_BAD_ARG) return 2;
+    if (smla_bwd_run_noalloc(NULL, NULL) != SMLA_ERR_BAD_ARG) return 3;
+    if (smla_bwd_staging_bytes_per_query(&p) != (size_t)2048 * SMLA_D_QK * 4) return 4;
+    printf("%s %zu\n", smla_status_string(SMLA_ERR_DEVICE_TIMEOUT), need);
+    return 0;
+}
+''')
+    exe = tmp_path / "abi"
+    cmd = ["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+           "-L", lib_dir, "-lsmla_bwd", "-Wl,-rpath," + lib_dir]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
+    assert "bounded wait" in run.stdout
