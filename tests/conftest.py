@@ -21,3 +21,17 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def import_extension():
+    """The compiled `mla_bwd_cuda` module; built in place first (`python setup.py build_ext --inplace`, about a minute)
+    when the tree does not hold it yet.  There is no Python stand-in: a failed build fails the test."""
+    import importlib
+    import subprocess
+    try:
+        return importlib.import_module("mla_bwd_cuda")
+    except ImportError:
+        res = subprocess.run([sys.executable, "setup.py", "build_ext", "--inplace"], cwd=ROOT, capture_output=True, text=True)
+        assert res.returncode == 0, "building mla_bwd_cuda failed:\n" + (res.stdout + res.stderr)[-3000:]
+        importlib.invalidate_caches()
+        return importlib.import_module("mla_bwd_cuda")

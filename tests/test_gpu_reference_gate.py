@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 
 
 def test_reference_gate_through_the_extension_module():
-    import mla_bwd_cuda                      # the compiled extension; no Python stand-in exists
+    from tests.conftest import import_extension
+    mla_bwd_cuda = import_extension()        # the compiled extension; no Python stand-in exists
     assert mla_bwd_cuda.__file__.endswith(".so")
     S, B_H, D_Q, S_KV, B_TOPK, D_V = 4096, 128, 576, 8192, 2048, 512
     torch.manual_seed(42)
@@ -52,7 +53,8 @@ def test_reference_gate_through_the_extension_module():
 
 
 def test_extension_keywords_and_errors():
-    import mla_bwd_cuda
+    from tests.conftest import import_extension
+    mla_bwd_cuda = import_extension()
     from test_operator_b200 import op
     from test_operator_b200.inputs import Workload, make_sequence
     w = Workload("ext", 1, 6, 256, 64, 128, "uniform", invalid_frac=0.1)
