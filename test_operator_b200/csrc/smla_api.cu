@@ -437,14 +437,14 @@ template <int HP>
 int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, cudaStream_t st) {
     using namespace smla;
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
-    CUtensorMap tm_qnh, tm_s;
+    CUtensorMap tm_qhp, tm_s;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
     bool ok = true;
-    ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
+    ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
     ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
-    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, 1>, rp::Cfg<HP, 1>::kSmemBytes);
-    attr_ok &= set_smem(smla_recompute_pair_kernel<HP, 2>, rp::Cfg<HP, 2>::kSmemBytes);
+    bool attr_ok = set_smem(smla_fwd_logits_kernel<HP, 1>, fl::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_fwd_logits_kernel<HP, 2>, fl::Cfg<HP>::kSmemBytes);
     // o = E.V: the two d-parts gather V column chunks [0,4) and [4,8)
     attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks, true>, dq::Cfg<HP>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
@@ -474,15 +474,16 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     const int n_rows = p->s_q * p->h_q;
     smla_fwd_stats_init_kernel<<<(n_rows + 255) / 256, 256, 0, st>>>(kp.m_ord, kp.l_fix, n_rows);
     ++g_last_launches;
-    const int pairs = resident_pairs(smla_recompute_pair_kernel<HP, 1>, rp::kThreads, rp::Cfg<HP, 1>::kSmemBytes);
-    if (pairs <= 0) return SMLA_ERR_LAUNCH;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return SMLA_ERR_LAUNCH;
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         kp.nq = nq;
-        const int grid = 2 * (nq < pairs ? nq : pairs);
-        smla_recompute_pair_kernel<HP, 1><<<grid, rp::kThreads, rp::Cfg<HP, 1>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
-        smla_recompute_pair_kernel<HP, 2><<<grid, rp::kThreads, rp::Cfg<HP, 2>::kSmemBytes, st>>>(tm_qnh, tm_qnh, kp);
+        const int grid = nq < sms ? nq : sms;       // one persistent CTA per SM (each takes the whole shared memory)
+        smla_fwd_logits_kernel<HP, 1><<<grid, fl::kThreads, fl::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, kp);
+        smla_fwd_logits_kernel<HP, 2><<<grid, fl::kThreads, fl::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, kp);
         smla_dq_kernel<HP, kVChunks / 2, kVChunks, true><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_s, kp);
         g_last_launches += 3;
     }

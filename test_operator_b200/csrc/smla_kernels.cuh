@@ -98,7 +98,7 @@ __device__ __forceinline__ size_t scratch_offset(int key, int head, int topk_pad
 
 
 // error codes recorded by bounded waits: 100*kernel + site
-enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300 };
+enum { kErrRecompute = 100, kErrDkv = 200, kErrDq = 300, kErrFwd = 400 };
 
 __device__ __forceinline__ bool slot_valid(int idx, int key, const QMeta& m, const KParams& p) {
     return key < m.topk_len && idx >= 0 && idx < m.kv_len && m.kv_base + idx < p.s_kv && (!p.causal || idx <= m.q_pos);
@@ -609,6 +609,339 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     __syncthreads();
     cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
     if (warp == 16) tmem_dealloc_2cta(tmem, C::kTmemCols);
+}
+
+// =============================================================================================
+// forward logits, one CTA per query (persistent, queries round-robin), single-CTA UMMAs.
+//
+// A pair UMMA (cta_group::2, M 256) occupies the issuing side for ~163 cycles whatever its N, a single-CTA UMMA of
+// M 128 x N 128 for its 64 cycles of math (measured, standalone).  With B = Q only there is no dO to share the
+// shared memory with, so a CTA can hold Q of ALL heads (9 x [HP heads x 64 col] = 144 KB at 128 heads) and work alone:
+//   A  the CTA's 128 gathered keys of a tile, chunk by chunk through a ring of [128 keys x 64 col] chunks
+//   B  Q_j of all heads;  D  [128 keys] x [HP heads] in TMEM, two buffers
+//   warps 0-7   row statistics / exponentials on the tile: warp w -> TMEM lane quarter w % 4, head half w / 4
+//   warps 8-15  gather producers (cp.async 16 B, swizzled)
+//   warps 16,17 the two UMMA issuers, alternate chunks, handing over through a counter
+//   warp 18     TMA of the query's Q chunks
+// kMode 1: row maxima only (atomicMax per head at the end of a query); kMode 2: E = exp2(logit - max) as bf16 into the
+// scratch (the backward's S layout) and the row sums in 2^-24 fixed point.
+// =============================================================================================
+namespace fl {
+constexpr int kThreads = 608;
+constexpr int kProducerThreads = 256;
+constexpr int kTileKeys = 128;
+constexpr int kChunkA = 128 * 128;
+template <int HP> struct Cfg {
+    static constexpr int kBChunk = HP * 128;                       // Q_j of all heads
+    static constexpr int kStages = HP == 128 ? 5 : 9;
+    static constexpr int kOffB = 0;
+    static constexpr int kOffRing = kQChunks * kBChunk;
+    static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
+    static constexpr int kSmemBytes = kOffMisc + 1024 + 512 + 1024;   // row maxima + barriers + alignment slack
+    static constexpr int kTmemCols = 2 * HP;                       // two accumulator buffers
+    static_assert(kSmemBytes <= 232448, "shared memory of one SM");
+};
+}  // namespace fl
+
+template <int HP, int kMode>
+__global__ void __launch_bounds__(fl::kThreads, 1)
+smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p) {
+    using namespace fl;
+    using C = Cfg<HP>;
+    constexpr int NH = HP / 2;
+    constexpr int kStages = C::kStages;
+    const int cta = blockIdx.x;
+    const int n_ctas = gridDim.x;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t s_base = smem_u32(smem);
+    uint8_t* misc = smem + C::kOffMisc;
+    float* m2_s = reinterpret_cast<float*>(misc);             // [HP] row maximum in base-2 units, +inf for padded heads
+    uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 1024);
+    const uint32_t bar_full = smem_u32(bars);               // [kStages] gathered chunk landed
+    const uint32_t bar_empty = bar_full + 8 * kStages;      // [kStages] the UMMAs reading the slot finished
+    const uint32_t bar_bfull = bar_empty + 8 * kStages;     // [9] Q column chunk of the current query landed
+    const uint32_t bar_bfree = bar_bfull + 8 * kQChunks;    // [9] the query's last UMMAs on the chunk finished
+    const uint32_t bar_tfull = bar_bfree + 8 * kQChunks;    // [2] accumulator buffer complete
+    const uint32_t bar_tempty = bar_tfull + 16;             // [2] the softmax warps have read the buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 4));
+    volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t tok = smem_u32(tmem_slot + 2);           // chunks issued so far, the issuers' hand-over
+    const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [2] one per issuer, used only while winding down after an abort
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 4) + 16 + 16 <= 512, "barrier area");
+    const WaitCtx wc{p.g_err, s_abort, p.wait_limit, 0u};
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        tmem_slot[2] = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(bar_full + 8 * i, kProducerThreads);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        for (int i = 0; i < kQChunks; ++i) {
+            mbar_init(bar_bfull + 8 * i, 1);
+            mbar_init(bar_bfree + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + 8 * i, 1);
+            mbar_init(bar_tempty + 8 * i, 8);    // eight softmax warps
+            mbar_init(bar_drain + 8 * i, 1);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 16) {
+        tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int n_tiles = p.topk_pad / kTileKeys;
+    const int nq = p.nq;
+
+    if (warp >= 8 && warp < 16) {
+        // ------------------------------------------------------------------ gather producers
+        const int pt = threadIdx.x - 256;   // 0..255
+        const int u = pt & 7;               // 16-byte unit inside a 128-byte chunk row
+        const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of the tile's 128 keys
+        const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
+        const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
+        const uint64_t pol_keep = l2_policy_evict_last();
+        // raw index values, loaded one tile ahead and turned into kv rows when they are used
+        QMeta qm_next = load_qmeta(p, p.q0 + (cta < nq ? cta : 0));
+        int idx_next[4];
+        auto load_idx = [&](int ql, int tile) {
+            if (ql >= nq) {
+                idx_next[0] = idx_next[1] = idx_next[2] = idx_next[3] = -1;
+                return;
+            }
+            if (tile == 0) qm_next = load_qmeta(p, p.q0 + ql);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = tile * kTileKeys + r0 + 32 * i;
+                idx_next[i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
+            }
+        };
+        load_idx(cta, 0);
+        int s = 0;
+        uint32_t ph = 1;                    // parity that means "slot free" for the current pass over the ring
+        for (int ql = cta; ql < nq; ql += n_ctas) {
+            for (int tile = 0; tile < n_tiles; ++tile) {
+                const char* src[4];
+                uint32_t nb[4];             // 0: slot out of range, read nothing and land zeros
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = gather_row(idx_next[i], qm_next, p);
+                    nb[i] = row >= 0 ? 16u : 0u;
+                    src[i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
+                }
+                if (tile + 1 < n_tiles) load_idx(ql, tile + 1);
+                else load_idx(ql + n_ctas, 0);
+                for (int j = 0; j < kQChunks; ++j) {
+                    mbar_wait(bar_empty + 8 * s, ph, wc, kErrFwd + 11, kPollSleepNs);
+                    const uint32_t d = dst0 + s * kChunkA;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
+                    cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+                    if (++s == kStages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 18) {
+        // ------------------------------------------------------------------ Q chunks of the query (all heads)
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            const uint64_t pol_stream = l2_policy_evict_first();
+            uint32_t qpar = 1;              // parity of "chunk free" left by the previous query
+            for (int ql = cta; ql < nq; ql += n_ctas, qpar ^= 1) {
+                const int row0 = (p.q0 + ql) * p.h_q;
+                for (int j = 0; j < kQChunks; ++j) {
+                    if (ql != cta) mbar_wait(bar_bfree + 8 * j, qpar, wc, kErrFwd + 16, kPollSleepNs);
+                    mbar_arrive_expect_tx(bar_bfull + 8 * j, C::kBChunk);
+                    tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_bfull + 8 * j, pol_stream);
+                }
+            }
+        }
+    } else if (warp == 16 || warp == 17) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ UMMA issuers
+            // Issuer x takes the chunks whose running number is x mod 2; the counter keeps the UMMAs in chunk order.
+            const int x = warp - 16;
+            constexpr uint32_t idesc = make_idesc_bf16(128, HP, 0, 0);
+            const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
+            const uint32_t desc_lo = static_cast<uint32_t>(make_smem_desc(0, 16, 1024, kSwizzle128));
+            const uint32_t a_lo0 = desc_lo + ((s_base + C::kOffRing) >> 4);
+            const uint32_t b_lo0 = desc_lo + ((s_base + C::kOffB) >> 4);
+            const int n_queries = nq > cta ? (nq - cta + n_ctas - 1) / n_ctas : 0;
+            const int total = n_queries * n_tiles * kQChunks;
+            int j = x, tile = 0, gt = 0;
+            uint32_t qpar = 0;
+            int s = x % kStages;
+            uint32_t ph = 0;
+            for (int it = x; it < total; it += 2) {
+                const int b = gt & 1;
+                if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gt >> 1) & 1) ^ 1, wc, kErrFwd + 13);
+                if (tile == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrFwd + 12);
+                mbar_spin(bar_full + 8 * s, ph, wc, kErrFwd + 14);
+                fence_proxy_async_smem();        // the chunk was written by cp.async, the tensor core reads it
+                flag_wait(tok, static_cast<uint32_t>(it), wc, kErrFwd + 19);
+                tc_fence_after_sync();
+                const uint32_t d = tmem + b * HP;
+                const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
+                const uint32_t b_lo = b_lo0 + j * (C::kBChunk >> 4);
+                umma_ss(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
+#pragma unroll
+                for (int kk = 1; kk < 4; ++kk)   // 32 bytes further along K = +2 in the address field
+                    umma_ss(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
+                tc_fence_before_sync();
+                flag_store(tok, static_cast<uint32_t>(it + 1));
+                umma_commit(bar_empty + 8 * s);
+                if (tile == n_tiles - 1) umma_commit(bar_bfree + 8 * j);
+                if (j == kQChunks - 1) umma_commit(bar_tfull + 8 * b);
+                j += 2;
+                if (j >= kQChunks) {
+                    j -= kQChunks;
+                    ++gt;
+                    if (++tile == n_tiles) {
+                        tile = 0;
+                        qpar ^= 1;
+                    }
+                }
+                s += 2;
+                if (s >= kStages) {
+                    s -= kStages;
+                    ph ^= 1;
+                }
+            }
+            if (*s_abort) {
+                umma_commit(bar_drain + 8 * x);
+                mbar_wait_drain(bar_drain + 8 * x, 0, p.wait_limit);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ row statistics / exponentials
+        const int quarter = warp & 3;
+        const int g = warp >> 2;            // head half
+        const int row = quarter * 32 + lane;
+        const uint64_t pol_stream = l2_policy_evict_first();
+        const int t = threadIdx.x;
+        // second pass: the row maximum found by the first pass, in base-2 units, fetched one query ahead
+        auto load_stat = [&](int ql) -> float {
+            if (kMode == 1 || ql >= nq || t >= HP) return 0.f;
+            if (t >= p.h_q) return __int_as_float(0x7f800000);
+            return ordered_to_float(p.m_ord[static_cast<size_t>(p.q0 + ql) * p.h_q + t]) * p.scale_log2e;
+        };
+        float stat_next = load_stat(cta);
+        int gt = 0;
+        for (int ql = cta; ql < nq; ql += n_ctas) {
+            const int qg = p.q0 + ql;
+            const QMeta qm = load_qmeta(p, qg);
+            if constexpr (kMode == 2) {
+                asm volatile("bar.sync 1, 256;" ::: "memory");      // every softmax warp is done with the previous query
+                if (t < HP) m2_s[t] = stat_next;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                stat_next = load_stat(ql + n_ctas);
+            }
+            // what this lane keeps for heads g * NH + lane and g * NH + 32 + lane over the query's tiles
+            float keep_max[2] = {__int_as_float(0xff800000), __int_as_float(0xff800000)};
+            unsigned long long keep_sum[2] = {0ull, 0ull};
+            for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
+                const int key = tile * kTileKeys + row;
+                const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
+                const bool valid = slot_valid(idx, key, qm, p);
+                const int b = gt & 1;
+                mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrFwd + 18, kPollSleepNs);
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * HP + g * NH;
+                if constexpr (kMode == 1) {
+                    // the maximum over the warp's 32 keys of every head: one warp reduction per head
+                    const float ninf = __int_as_float(0xff800000);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < NH; c0 += 32) {
+                        uint32_t pv[32];
+                        tmem_ld_32x32(taddr + c0, pv);
+                        tmem_ld_wait();
+                        float mine = ninf;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const float r = redux_max_f32(valid ? __uint_as_float(pv[c]) : ninf);
+                            if (lane == c) mine = r;
+                        }
+                        if (c0 == 0) keep_max[0] = fmaxf(keep_max[0], mine);
+                        else keep_max[1] = fmaxf(keep_max[1], mine);
+                    }
+                } else {
+                    const size_t off = static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
+                    __nv_bfloat16* s_out = p.s_scr + off;
+                    const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < NH; c0 += 16) {
+                        uint32_t pv[16];
+                        tmem_ld_32x16(taddr + c0, pv);
+                        tmem_ld_wait();
+                        uint32_t so[8];
+                        const float4* l4 = reinterpret_cast<const float4*>(m2_s + g * NH + c0);
+                        unsigned mine = 0;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const float4 l = l4[v];
+                            const float lv[4] = {l.x, l.y, l.z, l.w};
+                            float sv[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int c = 4 * v + e;
+                                // E <= 1 (+ one rounding): the same logits produced the maximum in the first pass
+                                const float ex = ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e]));
+                                sv[e] = ex;
+                                // row sums in 2^-24 fixed point: integer warp reductions and integer atomics add in
+                                // any order to the same result, and 2048 terms lose at most 2^-13 of a sum >= 1
+                                const unsigned fx = valid ? __float2uint_rz(ex * kFixScale) : 0u;
+                                const unsigned r = redux_add_u32(fx);
+                                if (lane == ((c0 + c) & 31)) mine = r;
+                            }
+                            so[2 * v] = pack_bf16x2(sv[0], sv[1]) & vmask;
+                            so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]) & vmask;
+                        }
+                        // columns c0 .. c0 + 15 went to lanes (c0 & 31) .. (c0 & 31) + 15
+                        if (static_cast<unsigned>(lane - (c0 & 31)) < 16u) {
+                            if (c0 < 32) keep_sum[0] += mine;
+                            else keep_sum[1] += mine;
+                        }
+                        __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
+                        const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
+                        st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
+                        st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * b);     // the accumulator reads have completed
+            }
+            // this warp's share of the query's row statistics: integer atomics, so the order in which the warps
+            // arrive does not change the result
+#pragma unroll
+            for (int k = 0; k < NH / 32; ++k) {
+                const int head = g * NH + 32 * k + lane;
+                if (head < p.h_q) {
+                    const size_t o = static_cast<size_t>(qg) * p.h_q + head;
+                    if constexpr (kMode == 1) atomicMax(p.m_ord + o, float_to_ordered(keep_max[k]));
+                    else atomicAdd(p.l_fix + o, keep_sum[k]);
+                }
+            }
+        }
+    }
+    abort_wind_down(s_abort);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 16) tmem_dealloc(tmem, C::kTmemCols);
 }
 
 // Row statistics of the forward start at -inf (maximum) and 0 (sum).
