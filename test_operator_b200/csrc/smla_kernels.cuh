@@ -618,11 +618,16 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 // M 128 x N 128 for its 64 cycles of math (measured, standalone).  With B = Q only there is no dO to share the
 // shared memory with, so a CTA can hold Q of ALL heads (9 x [HP heads x 64 col] = 144 KB at 128 heads) and work alone:
 //   A  the CTA's 128 gathered keys of a tile, chunk by chunk through a ring of [128 keys x 64 col] chunks
-//   B  Q_j of all heads;  D  [128 keys] x [HP heads] in TMEM, two buffers
+//   B  Q_j of all heads;  D  [128 keys] x [HP heads] in TMEM, four buffers
 //   warps 0-7   row statistics / exponentials on the tile: warp w -> TMEM lane quarter w % 4, head half w / 4
 //   warps 8-15  gather producers (cp.async 16 B, swizzled)
-//   warps 16,17 the two UMMA issuers, alternate chunks, handing over through a counter
+//   warps 16,17 the two UMMA issuers
 //   warp 18     TMA of the query's Q chunks
+// Two tiles are in flight at a time: the ring carries their chunks alternately (tile 2t chunk j, tile 2t+1 chunk j,
+// tile 2t chunk j+1, ...), issuer x takes every second ring position = the chunks of tile 2t + x, and accumulates into
+// a buffer of its own.  An accumulator is therefore written by one thread only, in chunk order, and the issuers need no
+// hand-over: while one does its bookkeeping the tensor pipe runs the other's UMMAs.  With two pairs of buffers the
+// statistics warps read one pair of tiles while the next pair accumulates.
 // kMode 1: row maxima only (atomicMax per head at the end of a query); kMode 2: E = exp2(logit - max) as bf16 into the
 // scratch (the backward's S layout) and the row sums in 2^-24 fixed point.
 // =============================================================================================
@@ -638,7 +643,7 @@ template <int HP> struct Cfg {
     static constexpr int kOffRing = kQChunks * kBChunk;
     static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
     static constexpr int kSmemBytes = kOffMisc + 1024 + 512 + 1024;   // row maxima + barriers + alignment slack
-    static constexpr int kTmemCols = 2 * HP;                       // two accumulator buffers
+    static constexpr int kTmemCols = 4 * HP;                       // two pairs of accumulator buffers
     static_assert(kSmemBytes <= 232448, "shared memory of one SM");
 };
 }  // namespace fl
@@ -665,31 +670,29 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     const uint32_t bar_empty = bar_full + 8 * kStages;      // [kStages] the UMMAs reading the slot finished
     const uint32_t bar_bfull = bar_empty + 8 * kStages;     // [9] Q column chunk of the current query landed
     const uint32_t bar_bfree = bar_bfull + 8 * kQChunks;    // [9] the query's last UMMAs on the chunk finished
-    const uint32_t bar_tfull = bar_bfree + 8 * kQChunks;    // [2] accumulator buffer complete
-    const uint32_t bar_tempty = bar_tfull + 16;             // [2] the softmax warps have read the buffer
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 4));
+    const uint32_t bar_tfull = bar_bfree + 8 * kQChunks;    // [4] accumulator buffer complete
+    const uint32_t bar_tempty = bar_tfull + 32;             // [4] the softmax warps have read the buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 8));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const uint32_t tok = smem_u32(tmem_slot + 2);           // chunks issued so far, the issuers' hand-over
     const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [2] one per issuer, used only while winding down after an abort
-    static_assert(8 * (2 * kStages + 2 * kQChunks + 4) + 16 + 16 <= 512, "barrier area");
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 8) + 16 + 16 <= 512, "barrier area");
     const WaitCtx wc{p.g_err, s_abort, p.wait_limit, 0u};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
-        tmem_slot[2] = 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(bar_full + 8 * i, kProducerThreads);
             mbar_init(bar_empty + 8 * i, 1);
         }
         for (int i = 0; i < kQChunks; ++i) {
             mbar_init(bar_bfull + 8 * i, 1);
-            mbar_init(bar_bfree + 8 * i, 1);
+            mbar_init(bar_bfree + 8 * i, 2);     // both issuers' last UMMAs on the chunk
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
             mbar_init(bar_tempty + 8 * i, 8);    // eight softmax warps
-            mbar_init(bar_drain + 8 * i, 1);
         }
+        for (int i = 0; i < 2; ++i) mbar_init(bar_drain + 8 * i, 1);
         fence_mbar_init();
     }
     if (warp == 16) {
@@ -700,7 +703,7 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const int n_tiles = p.topk_pad / kTileKeys;
+    const int n_tp = p.topk_pad / (2 * kTileKeys);      // tile pairs; the padded top-k is a multiple of 256
     const int nq = p.nq;
 
     if (warp >= 8 && warp < 16) {
@@ -711,46 +714,54 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
         const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
-        // raw index values, loaded one tile ahead and turned into kv rows when they are used
+        // raw index values, loaded one tile pair ahead and turned into kv rows when they are used
         QMeta qm_next = load_qmeta(p, p.q0 + (cta < nq ? cta : 0));
-        int idx_next[4];
-        auto load_idx = [&](int ql, int tile) {
+        int idx_next[2][4];
+        auto load_idx = [&](int ql, int tp) {
             if (ql >= nq) {
-                idx_next[0] = idx_next[1] = idx_next[2] = idx_next[3] = -1;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) idx_next[0][i] = idx_next[1][i] = -1;
                 return;
             }
-            if (tile == 0) qm_next = load_qmeta(p, p.q0 + ql);
+            if (tp == 0) qm_next = load_qmeta(p, p.q0 + ql);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = tile * kTileKeys + r0 + 32 * i;
-                idx_next[i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
-            }
+            for (int sub = 0; sub < 2; ++sub)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = (2 * tp + sub) * kTileKeys + r0 + 32 * i;
+                    idx_next[sub][i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
+                }
         };
         load_idx(cta, 0);
         int s = 0;
         uint32_t ph = 1;                    // parity that means "slot free" for the current pass over the ring
         for (int ql = cta; ql < nq; ql += n_ctas) {
-            for (int tile = 0; tile < n_tiles; ++tile) {
-                const char* src[4];
-                uint32_t nb[4];             // 0: slot out of range, read nothing and land zeros
+            for (int tp = 0; tp < n_tp; ++tp) {
+                const char* src[2][4];
+                uint32_t nb[2][4];          // 0: slot out of range, read nothing and land zeros
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = gather_row(idx_next[i], qm_next, p);
-                    nb[i] = row >= 0 ? 16u : 0u;
-                    src[i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
-                }
-                if (tile + 1 < n_tiles) load_idx(ql, tile + 1);
+                for (int sub = 0; sub < 2; ++sub)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int row = gather_row(idx_next[sub][i], qm_next, p);
+                        nb[sub][i] = row >= 0 ? 16u : 0u;
+                        src[sub][i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
+                    }
+                if (tp + 1 < n_tp) load_idx(ql, tp + 1);
                 else load_idx(ql + n_ctas, 0);
                 for (int j = 0; j < kQChunks; ++j) {
-                    mbar_wait(bar_empty + 8 * s, ph, wc, kErrFwd + 11, kPollSleepNs);
-                    const uint32_t d = dst0 + s * kChunkA;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        cp_async16_zfill_hint(d + i * 32 * 128, src[i] + j * 128, nb[i], pol_keep);
-                    cp_async_mbar_arrive_noinc(bar_full + 8 * s);
-                    if (++s == kStages) {
-                        s = 0;
-                        ph ^= 1;
+                    for (int sub = 0; sub < 2; ++sub) {
+                        mbar_wait(bar_empty + 8 * s, ph, wc, kErrFwd + 11, kPollSleepNs);
+                        const uint32_t d = dst0 + s * kChunkA;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            cp_async16_zfill_hint(d + i * 32 * 128, src[sub][i] + j * 128, nb[sub][i], pol_keep);
+                        cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+                        if (++s == kStages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
                     }
                 }
             }
@@ -773,7 +784,8 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     } else if (warp == 16 || warp == 17) {
         if (lane == 0) {
             // ------------------------------------------------------------------ UMMA issuers
-            // Issuer x takes the chunks whose running number is x mod 2; the counter keeps the UMMAs in chunk order.
+            // Issuer x takes the ring positions whose running number is x mod 2: the chunks of the pair's tile x,
+            // accumulated into buffer 2 * (pair parity) + x.
             const int x = warp - 16;
             constexpr uint32_t idesc = make_idesc_bf16(128, HP, 0, 0);
             const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
@@ -781,18 +793,17 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
             const uint32_t a_lo0 = desc_lo + ((s_base + C::kOffRing) >> 4);
             const uint32_t b_lo0 = desc_lo + ((s_base + C::kOffB) >> 4);
             const int n_queries = nq > cta ? (nq - cta + n_ctas - 1) / n_ctas : 0;
-            const int total = n_queries * n_tiles * kQChunks;
-            int j = x, tile = 0, gt = 0;
+            const int total = n_queries * n_tp * kQChunks;
+            int j = 0, tp = 0, gtp = 0;
             uint32_t qpar = 0;
-            int s = x % kStages;
+            int s = x;
             uint32_t ph = 0;
-            for (int it = x; it < total; it += 2) {
-                const int b = gt & 1;
-                if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gt >> 1) & 1) ^ 1, wc, kErrFwd + 13);
-                if (tile == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrFwd + 12);
+            for (int k = 0; k < total; ++k) {
+                const int b = 2 * (gtp & 1) + x;
+                if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gtp >> 1) & 1) ^ 1, wc, kErrFwd + 13);
+                if (tp == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrFwd + 12);
                 mbar_spin(bar_full + 8 * s, ph, wc, kErrFwd + 14);
                 fence_proxy_async_smem();        // the chunk was written by cp.async, the tensor core reads it
-                flag_wait(tok, static_cast<uint32_t>(it), wc, kErrFwd + 19);
                 tc_fence_after_sync();
                 const uint32_t d = tmem + b * HP;
                 const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
@@ -801,17 +812,14 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
 #pragma unroll
                 for (int kk = 1; kk < 4; ++kk)   // 32 bytes further along K = +2 in the address field
                     umma_ss(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
-                tc_fence_before_sync();
-                flag_store(tok, static_cast<uint32_t>(it + 1));
                 umma_commit(bar_empty + 8 * s);
-                if (tile == n_tiles - 1) umma_commit(bar_bfree + 8 * j);
+                if (tp == n_tp - 1) umma_commit(bar_bfree + 8 * j);
                 if (j == kQChunks - 1) umma_commit(bar_tfull + 8 * b);
-                j += 2;
-                if (j >= kQChunks) {
-                    j -= kQChunks;
-                    ++gt;
-                    if (++tile == n_tiles) {
-                        tile = 0;
+                if (++j == kQChunks) {
+                    j = 0;
+                    ++gtp;
+                    if (++tp == n_tp) {
+                        tp = 0;
                         qpar ^= 1;
                     }
                 }
@@ -840,7 +848,8 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
             return ordered_to_float(p.m_ord[static_cast<size_t>(p.q0 + ql) * p.h_q + t]) * p.scale_log2e;
         };
         float stat_next = load_stat(cta);
-        int gt = 0;
+        int gt = 0;                         // tiles so far: pair gt >> 1, tile gt & 1 of the pair
+        const int n_tiles = 2 * n_tp;
         for (int ql = cta; ql < nq; ql += n_ctas) {
             const int qg = p.q0 + ql;
             const QMeta qm = load_qmeta(p, qg);
@@ -857,8 +866,8 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                 const int key = tile * kTileKeys + row;
                 const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
                 const bool valid = slot_valid(idx, key, qm, p);
-                const int b = gt & 1;
-                mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrFwd + 18, kPollSleepNs);
+                const int b = gt & 3;               // 2 * (pair parity) + tile of the pair
+                mbar_wait(bar_tfull + 8 * b, (gt >> 2) & 1, wc, kErrFwd + 18, kPollSleepNs);
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * HP + g * NH;
                 if constexpr (kMode == 1) {
