@@ -264,7 +264,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     if (!ok) return SMLA_ERR_LAUNCH;
 
     // per device, so set on every call (cheap) rather than once per process
-    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP, 0>, rp::Cfg<HP, 0>::kSmemBytes);
+    bool attr_ok = set_smem(smla_recompute_pair_kernel<HP>, rp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_pair_kernel<HP>, dp::Cfg<HP>::kSmemBytes);
     if (det) attr_ok &= set_smem(smla_dkv_pair_kernel<HP, true>, dp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dq_kernel<HP, kSplitChunk, kQChunks>, dq::Cfg<HP>::kSmemBytes);
@@ -302,11 +302,11 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
                                                           reinterpret_cast<const uint4*>(p->dO), delta, n_rows);
         ++g_last_launches;
     }
-    const int pairs_r = resident_pairs(smla_recompute_pair_kernel<HP, 0>, rp::kThreads, rp::Cfg<HP, 0>::kSmemBytes);
+    const int pairs_r = resident_pairs(smla_recompute_pair_kernel<HP>, rp::kThreads, rp::Cfg<HP>::kSmemBytes);
     const int pairs_d = resident_pairs(smla_dkv_pair_kernel<HP>, dp::kThreads, dp::Cfg<HP>::kSmemBytes);
     if (pairs_r <= 0 || pairs_d <= 0) return SMLA_ERR_LAUNCH;
     auto launch_recompute = [&](cudaStream_t s_, int pairs) {
-        smla_recompute_pair_kernel<HP, 0><<<2 * (kp.nq < pairs ? kp.nq : pairs), rp::kThreads, rp::Cfg<HP, 0>::kSmemBytes, s_>>>(tm_qnh, tm_donh, kp);
+        smla_recompute_pair_kernel<HP><<<2 * (kp.nq < pairs ? kp.nq : pairs), rp::kThreads, rp::Cfg<HP>::kSmemBytes, s_>>>(tm_qnh, tm_donh, kp);
         ++g_last_launches;
     };
     auto launch_dkv = [&](cudaStream_t s_, int pairs) {

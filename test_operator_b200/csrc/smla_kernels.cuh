@@ -175,32 +175,26 @@ constexpr int kThreads = 608;
 constexpr int kProducerThreads = 256;
 constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;         // 16 KB gathered chunk
-// kMode 0: backward recompute (B = [Q | dO], outputs bf16 S and dS)
-// kMode 1: forward, first pass  (B = Q only): row maxima of the logits, nothing else is written
-// kMode 2: forward, second pass (B = Q only): E = exp2(logit - max) as bf16 into the S scratch, and its row sums
-// In the forward passes the shared memory dO would take goes to a deeper gather ring.
-template <int HP, int kMode> struct Cfg {
-    static constexpr bool kFwd = kMode != 0;
+template <int HP> struct Cfg {
     static constexpr int NH = HP / 2;                  // heads whose Q / dO rows this CTA holds
-    static constexpr int kStages = kFwd ? 9 : 5;
+    static constexpr int kStages = 5;
     static constexpr int kBHalf = NH * 128;            // one [NH heads x 64 col] chunk
-    static constexpr int kBChunk = kFwd ? kBHalf : 2 * kBHalf;   // Q_j alone, or stacked [Q_j | dO_j]
+    static constexpr int kBChunk = 2 * kBHalf;         // stacked [Q_j | dO_j]
     static constexpr int kOffB = 0;
     static constexpr int kOffRing = kQChunks * kBChunk;
     static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
     static constexpr int kSmemBytes = kOffMisc + 1024 + 512 + 1024;   // lse/delta + barriers + alignment slack
-    static constexpr int kAccCols = kFwd ? HP : 2 * HP;            // one accumulator buffer
+    static constexpr int kAccCols = 2 * HP;                        // one accumulator buffer: [S | dP]
     static constexpr int kTmemCols = 2 * kAccCols;                 // two buffers
 };
 }  // namespace rp
 
-template <int HP, int kMode>
+template <int HP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(rp::kThreads, 1)
 smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                            const KParams p) {
     using namespace rp;
-    using C = Cfg<HP, kMode>;
-    constexpr bool kFwd = kMode != 0;
+    using C = Cfg<HP>;
     constexpr int NH = C::NH;
     constexpr int kStages = C::kStages;
     const uint32_t rank = cluster_ctarank();
@@ -248,7 +242,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         }
         fence_mbar_init();
     }
-    if constexpr (!kFwd) {   // zero block standing in for the dO half of column chunk 8 (never overwritten)
+    {   // zero block standing in for the dO half of column chunk 8 (never overwritten)
         uint4* z = reinterpret_cast<uint4*>(smem + C::kOffB + 8 * C::kBChunk + C::kBHalf);
         for (int i = threadIdx.x; i < C::kBHalf / 16; i += kThreads) z[i] = make_uint4(0, 0, 0, 0);
         fence_proxy_async_smem();
@@ -334,7 +328,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const int row0 = (p.q0 + ql) * p.h_q + NH * rank;
                 for (int j = 0; j < kQChunks; ++j) {
                     if (ql != pair) mbar_wait(bar_bfree + 8 * j, qpar, wc, kErrRecompute + 16, kPollSleepNs);
-                    const bool with_do = !kFwd && j < kVChunks;
+                    const bool with_do = j < kVChunks;
                     mbar_arrive_expect_tx(bar_bfull + 8 * j, (with_do ? 2 : 1) * C::kBHalf);
                     tma_load_2d_hint(s_base + C::kOffB + j * C::kBChunk, &tm_q, 64 * j, row0, bar_bfull + 8 * j, pol_stream);
                     if (with_do)
@@ -439,14 +433,12 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         // lse (threads 0..HP-1) and Delta (threads HP..2HP-1) of a query go through shared memory; the value for
         // the next query is fetched one query ahead
         const int t = threadIdx.x;
-        // (forward, second pass: the row maximum found by the first pass takes the place of lse, in base-2 units)
         auto load_stat = [&](int ql) -> float {
-            if (kMode == 1 || ql >= nq) return 0.f;
+            if (ql >= nq) return 0.f;
             const int h = t < HP ? t : t - HP;
             if (t >= 2 * HP) return 0.f;
             if (h >= p.h_q) return t < HP ? __int_as_float(0x7f800000) : 0.f;
             const size_t o = static_cast<size_t>(p.q0 + ql) * p.h_q + h;
-            if constexpr (kMode == 2) return t < HP ? ordered_to_float(p.m_ord[o]) * p.scale_log2e : 0.f;
             return t < HP ? p.lse[o] * p.lse_mult : p.delta[o] * p.sm_scale;
         };
         float stat_next = load_stat(pair);
@@ -454,15 +446,10 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         for (int ql = pair; ql < nq; ql += n_pairs) {
             const int qg = p.q0 + ql;
             const QMeta qm = load_qmeta(p, qg);
-            if constexpr (kMode != 1) {
-                asm volatile("bar.sync 1, 256;" ::: "memory");      // every softmax warp is done with the previous query
-                if (t < 2 * HP) lse_s[t] = stat_next;              // delta_s follows lse_s
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                stat_next = load_stat(ql + n_pairs);
-            }
-            // forward: what this lane keeps for heads g * NH + lane and g * NH + 32 + lane over the query's tiles
-            float keep_max[2] = {__int_as_float(0xff800000), __int_as_float(0xff800000)};
-            unsigned long long keep_sum[2] = {0ull, 0ull};
+            asm volatile("bar.sync 1, 256;" ::: "memory");      // every softmax warp is done with the previous query
+            if (t < 2 * HP) lse_s[t] = stat_next;              // delta_s follows lse_s
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            stat_next = load_stat(ql + n_pairs);
             for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
                 const int key = tile * kTileKeys + rank * 128 + row;
                 const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
@@ -470,69 +457,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const int b = gt & 1;
                 mbar_wait(bar_tfull + 8 * b, (gt >> 1) & 1, wc, kErrRecompute + 18, kPollSleepNs);
                 tc_fence_after_sync();
-                if constexpr (kMode == 1) {
-                    // accumulator columns: [heads of the even CTA | heads of the odd CTA] = head order.  The maximum
-                    // over the warp's 32 keys of every head comes from one integer warp reduction per head.
-                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
-                    const float ninf = __int_as_float(0xff800000);
-#pragma unroll 1
-                    for (int c0 = 0; c0 < NH; c0 += 32) {
-                        uint32_t pv[32];
-                        tmem_ld_32x32(taddr + c0, pv);
-                        tmem_ld_wait();
-                        float mine = ninf;
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const float r = redux_max_f32(valid ? __uint_as_float(pv[c]) : ninf);
-                            if (lane == c) mine = r;
-                        }
-                        if (c0 == 0) keep_max[0] = fmaxf(keep_max[0], mine);
-                        else keep_max[1] = fmaxf(keep_max[1], mine);
-                    }
-                } else if constexpr (kMode == 2) {
-                    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * NH;
-                    const size_t off = static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
-                    __nv_bfloat16* s_out = p.s_scr + off;
-                    const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < NH; c0 += 16) {
-                        uint32_t pv[16];
-                        tmem_ld_32x16(taddr + c0, pv);
-                        tmem_ld_wait();
-                        uint32_t so[8];
-                        const float4* l4 = reinterpret_cast<const float4*>(lse_s + g * NH + c0);
-                        unsigned mine = 0;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const float4 l = l4[v];
-                            const float lv[4] = {l.x, l.y, l.z, l.w};
-                            float sv[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int c = 4 * v + e;
-                                // E <= 1 (+ one rounding): the same logits produced the maximum in the first pass
-                                const float ex = ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e]));
-                                sv[e] = ex;
-                                // row sums in 2^-24 fixed point: integer warp reductions and integer atomics add in
-                                // any order to the same result, and 2048 terms lose at most 2^-13 of a sum >= 1
-                                const unsigned fx = valid ? __float2uint_rz(ex * kFixScale) : 0u;
-                                const unsigned r = redux_add_u32(fx);
-                                if (lane == ((c0 + c) & 31)) mine = r;
-                            }
-                            so[2 * v] = pack_bf16x2(sv[0], sv[1]) & vmask;
-                            so[2 * v + 1] = pack_bf16x2(sv[2], sv[3]) & vmask;
-                        }
-                        // columns c0 .. c0 + 15 went to lanes (c0 & 31) .. (c0 & 31) + 15
-                        if (static_cast<unsigned>(lane - (c0 & 31)) < 16u) {
-                            if (c0 < 32) keep_sum[0] += mine;
-                            else keep_sum[1] += mine;
-                        }
-                        __nv_bfloat16* s0 = s_out + static_cast<size_t>(c0) * p.topk_pad;
-                        const size_t blk = static_cast<size_t>(p.topk_pad) * 8;
-                        st_global_v4_hint(s0, so[0], so[1], so[2], so[3], pol_stream);
-                        st_global_v4_hint(s0 + blk, so[4], so[5], so[6], so[7], pol_stream);
-                    }
-                } else {
+                {
                     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + b * C::kAccCols + g * 2 * NH;
                     // the 32 lanes hold consecutive keys: 32 x 16 bytes of consecutive addresses per store
                     const size_t off = static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
@@ -589,19 +514,6 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 // the warp for about a thousand cycles per tile.
                 if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * b);
             }
-            if constexpr (kFwd) {
-                // this warp's share of the query's row statistics: integer atomics, so the order in which the eight
-                // warps of the two CTAs arrive does not change the result
-#pragma unroll
-                for (int k = 0; k < NH / 32; ++k) {
-                    const int head = g * NH + 32 * k + lane;
-                    if (head < p.h_q) {
-                        const size_t o = static_cast<size_t>(qg) * p.h_q + head;
-                        if constexpr (kMode == 1) atomicMax(p.m_ord + o, float_to_ordered(keep_max[k]));
-                        else atomicAdd(p.l_fix + o, keep_sum[k]);
-                    }
-                }
-            }
         }
     }
     abort_wind_down(s_abort);
@@ -620,20 +532,25 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 //   A  the CTA's 128 gathered keys of a tile, chunk by chunk through a ring of [128 keys x 64 col] chunks
 //   B  Q_j of all heads;  D  [128 keys] x [HP heads] in TMEM, four buffers
 //   warps 0-7   row statistics / exponentials on the tile: warp w -> TMEM lane quarter w % 4, head half w / 4
-//   warps 8-15  gather producers (cp.async 16 B, swizzled)
-//   warps 16,17 the two UMMA issuers
-//   warp 18     TMA of the query's Q chunks
+//   warps 8-11  gather producers (cp.async 16 B, swizzled)
+//   warps 12-15 the four UMMA issuers
+//   warp 16     TMA of the query's Q chunks
 // Two tiles are in flight at a time: the ring carries their chunks alternately (tile 2t chunk j, tile 2t+1 chunk j,
-// tile 2t chunk j+1, ...), issuer x takes every second ring position = the chunks of tile 2t + x, and accumulates into
-// a buffer of its own.  An accumulator is therefore written by one thread only, in chunk order, and the issuers need no
-// hand-over: while one does its bookkeeping the tensor pipe runs the other's UMMAs.  With two pairs of buffers the
-// statistics warps read one pair of tiles while the next pair accumulates.
+// tile 2t chunk j+1, ...): the even ring positions are the chunk stream of the even tiles, the odd positions that of the
+// odd tiles, and each stream accumulates into buffers of its own.  With two pairs of buffers the statistics warps read
+// one pair of tiles while the next pair accumulates.
+// A thread that issues UMMAs executes everything slowly (measured in this kernel: ~370 cycles for the four UMMAs of a
+// chunk, ~240 for its commits, ~200 for advancing a handful of counters, ~1050 per chunk in all, against 256 cycles of
+// tensor-pipe time), so a stream is shared by two issuers that take alternate chunks: four threads, each with
+// 4 x 256 cycles per chunk of its own.  The two issuers of a stream hand over through a counter in shared memory, so
+// the UMMAs of an accumulator enter the pipe in chunk order and the result is reproducible bit for bit; the streams
+// are independent of each other.
 // kMode 1: row maxima only (atomicMax per head at the end of a query); kMode 2: E = exp2(logit - max) as bf16 into the
 // scratch (the backward's S layout) and the row sums in 2^-24 fixed point.
 // =============================================================================================
 namespace fl {
-constexpr int kThreads = 608;
-constexpr int kProducerThreads = 256;
+constexpr int kProducerThreads = 128;
+constexpr int kThreads = 256 + kProducerThreads + 128 + 32;   // statistics, producers, issuers, Q loader
 constexpr int kTileKeys = 128;
 constexpr int kChunkA = 128 * 128;
 template <int HP> struct Cfg {
@@ -674,12 +591,14 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     const uint32_t bar_tempty = bar_tfull + 32;             // [4] the softmax warps have read the buffer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 8));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [2] one per issuer, used only while winding down after an abort
-    static_assert(8 * (2 * kStages + 2 * kQChunks + 8) + 16 + 16 <= 512, "barrier area");
+    const uint32_t tok = smem_u32(tmem_slot + 2);           // [2] chunks issued so far in each stream: the issuers' hand-over
+    const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [4] one per issuer, used only while winding down after an abort
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 8) + 16 + 32 <= 512, "barrier area");
     const WaitCtx wc{p.g_err, s_abort, p.wait_limit, 0u};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
+        tmem_slot[2] = tmem_slot[3] = 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(bar_full + 8 * i, kProducerThreads);
             mbar_init(bar_empty + 8 * i, 1);
@@ -692,10 +611,10 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
             mbar_init(bar_tfull + 8 * i, 1);
             mbar_init(bar_tempty + 8 * i, 8);    // eight softmax warps
         }
-        for (int i = 0; i < 2; ++i) mbar_init(bar_drain + 8 * i, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bar_drain + 8 * i, 1);
         fence_mbar_init();
     }
-    if (warp == 16) {
+    if (warp == 12) {
         tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
         tmem_relinquish();
     }
@@ -706,29 +625,29 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     const int n_tp = p.topk_pad / (2 * kTileKeys);      // tile pairs; the padded top-k is a multiple of 256
     const int nq = p.nq;
 
-    if (warp >= 8 && warp < 16) {
+    if (warp >= 8 && warp < 12) {
         // ------------------------------------------------------------------ gather producers
-        const int pt = threadIdx.x - 256;   // 0..255
+        const int pt = threadIdx.x - 256;   // 0..127
         const int u = pt & 7;               // 16-byte unit inside a 128-byte chunk row
-        const int r0 = pt >> 3;             // rows r0, r0+32, r0+64, r0+96 of the tile's 128 keys
+        const int r0 = pt >> 3;             // rows r0 + 16 i of the tile's 128 keys
         const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
         // raw index values, loaded one tile pair ahead and turned into kv rows when they are used
         QMeta qm_next = load_qmeta(p, p.q0 + (cta < nq ? cta : 0));
-        int idx_next[2][4];
+        int idx_next[2][8];
         auto load_idx = [&](int ql, int tp) {
             if (ql >= nq) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) idx_next[0][i] = idx_next[1][i] = -1;
+                for (int i = 0; i < 8; ++i) idx_next[0][i] = idx_next[1][i] = -1;
                 return;
             }
             if (tp == 0) qm_next = load_qmeta(p, p.q0 + ql);
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int key = (2 * tp + sub) * kTileKeys + r0 + 32 * i;
+                for (int i = 0; i < 8; ++i) {
+                    const int key = (2 * tp + sub) * kTileKeys + r0 + 16 * i;
                     idx_next[sub][i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
                 }
         };
@@ -737,16 +656,11 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
         uint32_t ph = 1;                    // parity that means "slot free" for the current pass over the ring
         for (int ql = cta; ql < nq; ql += n_ctas) {
             for (int tp = 0; tp < n_tp; ++tp) {
-                const char* src[2][4];
-                uint32_t nb[2][4];          // 0: slot out of range, read nothing and land zeros
+                int row[2][8];              // kv row, or -1: slot out of range, read nothing and land zeros
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int row = gather_row(idx_next[sub][i], qm_next, p);
-                        nb[sub][i] = row >= 0 ? 16u : 0u;
-                        src[sub][i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
-                    }
+                    for (int i = 0; i < 8; ++i) row[sub][i] = gather_row(idx_next[sub][i], qm_next, p);
                 if (tp + 1 < n_tp) load_idx(ql, tp + 1);
                 else load_idx(ql + n_ctas, 0);
                 for (int j = 0; j < kQChunks; ++j) {
@@ -755,8 +669,11 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                         mbar_wait(bar_empty + 8 * s, ph, wc, kErrFwd + 11, kPollSleepNs);
                         const uint32_t d = dst0 + s * kChunkA;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            cp_async16_zfill_hint(d + i * 32 * 128, src[sub][i] + j * 128, nb[sub][i], pol_keep);
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = row[sub][i];
+                            cp_async16_zfill_hint(d + i * 16 * 128, kvb + static_cast<size_t>(r >= 0 ? r : 0) * (kDQK * 2) + j * 128,
+                                                  r >= 0 ? 16u : 0u, pol_keep);
+                        }
                         cp_async_mbar_arrive_noinc(bar_full + 8 * s);
                         if (++s == kStages) {
                             s = 0;
@@ -766,7 +683,7 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                 }
             }
         }
-    } else if (warp == 18) {
+    } else if (warp == 16) {
         // ------------------------------------------------------------------ Q chunks of the query (all heads)
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
@@ -781,29 +698,32 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                 }
             }
         }
-    } else if (warp == 16 || warp == 17) {
+    } else if (warp >= 12 && warp < 16) {
         if (lane == 0) {
             // ------------------------------------------------------------------ UMMA issuers
-            // Issuer x takes the ring positions whose running number is x mod 2: the chunks of the pair's tile x,
-            // accumulated into buffer 2 * (pair parity) + x.
-            const int x = warp - 16;
+            // Issuer i takes the ring positions i, i + 4, ...: chunks y, y + 2, ... (y = i / 2) of stream x = i % 2, the
+            // tiles 2t + x, accumulated into buffer 2 * (pair parity) + x.
+            const int i = warp - 12;
+            const int x = i & 1, y = i >> 1;
             constexpr uint32_t idesc = make_idesc_bf16(128, HP, 0, 0);
             const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
             const uint32_t desc_lo = static_cast<uint32_t>(make_smem_desc(0, 16, 1024, kSwizzle128));
             const uint32_t a_lo0 = desc_lo + ((s_base + C::kOffRing) >> 4);
             const uint32_t b_lo0 = desc_lo + ((s_base + C::kOffB) >> 4);
             const int n_queries = nq > cta ? (nq - cta + n_ctas - 1) / n_ctas : 0;
-            const int total = n_queries * n_tp * kQChunks;
-            int j = 0, tp = 0, gtp = 0;
+            const int total = n_queries * n_tp * kQChunks;      // chunks of a stream
+            const uint32_t my_tok = tok + 4 * x;
+            int j = y, tp = 0, gtp = 0;
             uint32_t qpar = 0;
-            int s = x;
+            int s = i;
             uint32_t ph = 0;
-            for (int k = 0; k < total; ++k) {
+            for (int c = y; c < total; c += 2) {
                 const int b = 2 * (gtp & 1) + x;
                 if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gtp >> 1) & 1) ^ 1, wc, kErrFwd + 13);
                 if (tp == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrFwd + 12);
                 mbar_spin(bar_full + 8 * s, ph, wc, kErrFwd + 14);
                 fence_proxy_async_smem();        // the chunk was written by cp.async, the tensor core reads it
+                flag_wait(my_tok, static_cast<uint32_t>(c), wc, kErrFwd + 19);
                 tc_fence_after_sync();
                 const uint32_t d = tmem + b * HP;
                 const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
@@ -812,26 +732,31 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
 #pragma unroll
                 for (int kk = 1; kk < 4; ++kk)   // 32 bytes further along K = +2 in the address field
                     umma_ss(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
+                tc_fence_before_sync();
+                flag_store(my_tok, static_cast<uint32_t>(c + 1));
+                // The UMMAs on one accumulator complete in the order they were issued, so the commit behind a tile's
+                // last chunk covers the chunks the stream's other issuer put in before it.
                 umma_commit(bar_empty + 8 * s);
                 if (tp == n_tp - 1) umma_commit(bar_bfree + 8 * j);
                 if (j == kQChunks - 1) umma_commit(bar_tfull + 8 * b);
-                if (++j == kQChunks) {
-                    j = 0;
+                j += 2;
+                if (j >= kQChunks) {
+                    j -= kQChunks;
                     ++gtp;
                     if (++tp == n_tp) {
                         tp = 0;
                         qpar ^= 1;
                     }
                 }
-                s += 2;
+                s += 4;
                 if (s >= kStages) {
                     s -= kStages;
                     ph ^= 1;
                 }
             }
             if (*s_abort) {
-                umma_commit(bar_drain + 8 * x);
-                mbar_wait_drain(bar_drain + 8 * x, 0, p.wait_limit);
+                umma_commit(bar_drain + 8 * i);
+                mbar_wait_drain(bar_drain + 8 * i, 0, p.wait_limit);
             }
         }
     } else {
@@ -950,7 +875,7 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     abort_wind_down(s_abort);
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 16) tmem_dealloc(tmem, C::kTmemCols);
+    if (warp == 12) tmem_dealloc(tmem, C::kTmemCols);
 }
 
 // Row statistics of the forward start at -inf (maximum) and 0 (sum).
