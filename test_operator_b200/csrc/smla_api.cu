@@ -267,7 +267,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
     bool attr_ok = set_smem(smla_recompute_pair_kernel<HP>, rp::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_dkv_pair_kernel<HP>, dp::Cfg<HP>::kSmemBytes);
     if (det) attr_ok &= set_smem(smla_dkv_pair_kernel<HP, true>, dp::Cfg<HP>::kSmemBytes);
-    attr_ok &= set_smem(smla_dq_kernel<HP, kSplitChunk, kQChunks>, dq::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_dq_kernel<HP, kDqChunks, kQChunks>, dq::Cfg<HP, kDqChunks>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
     KParams kp{};
@@ -324,7 +324,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
         ++g_last_launches;
     };
     auto launch_dq = [&](cudaStream_t s_) {
-        smla_dq_kernel<HP, kSplitChunk, kQChunks><<<kp.nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, s_>>>(tm_ds, kp);
+        smla_dq_kernel<HP, kDqChunks, kQChunks><<<kp.nq * (kQChunks / kDqChunks), dq::kThreads, dq::Cfg<HP, kDqChunks>::kSmemBytes, s_>>>(tm_ds, kp);
         ++g_last_launches;
     };
 
@@ -446,7 +446,7 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     bool attr_ok = set_smem(smla_fwd_logits_kernel<HP, 1>, fl::Cfg<HP>::kSmemBytes);
     attr_ok &= set_smem(smla_fwd_logits_kernel<HP, 2>, fl::Cfg<HP>::kSmemBytes);
     // o = E.V: the two d-parts gather V column chunks [0,4) and [4,8)
-    attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks, true>, dq::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks, true>, dq::Cfg<HP, kVChunks / 2>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
 
     KParams kp{};
@@ -484,7 +484,7 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
         const int grid = nq < sms ? nq : sms;       // one persistent CTA per SM (each takes the whole shared memory)
         smla_fwd_logits_kernel<HP, 1><<<grid, fl::kThreads, fl::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, kp);
         smla_fwd_logits_kernel<HP, 2><<<grid, fl::kThreads, fl::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, kp);
-        smla_dq_kernel<HP, kVChunks / 2, kVChunks, true><<<nq * 2, dq::kThreads, dq::Cfg<HP>::kSmemBytes, st>>>(tm_s, kp);
+        smla_dq_kernel<HP, kVChunks / 2, kVChunks, true><<<nq * 2, dq::kThreads, dq::Cfg<HP, kVChunks / 2>::kSmemBytes, st>>>(tm_s, kp);
         g_last_launches += 3;
     }
     return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;

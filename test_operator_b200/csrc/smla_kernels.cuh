@@ -32,7 +32,7 @@ constexpr int kDQK = 576;
 constexpr int kDV = 512;
 constexpr int kQChunks = kDQK / 64;   // 9 column chunks of 64
 constexpr int kVChunks = kDV / 64;    // 8
-constexpr int kSplitChunk = 5;        // d-part 0 = chunks [0,5) = columns [0,320); part 1 = chunks [5,9)
+constexpr int kDqChunks = 3;          // dq: three d-parts of three column chunks (192 columns) each
 
 struct KParams {
     const __nv_bfloat16* kv;  // [s_kv, 576]
@@ -1256,7 +1256,8 @@ __global__ void __launch_bounds__(256) smla_dkv_segment_sum_kernel(const int* __
 }
 
 // =============================================================================================
-// dq: one CTA per (query, d-part); same d split as dkv; 14 warps.
+// dq: one CTA per (query, d-part of kSplit column chunks); 14 warps; two CTAs per SM, so that one's start-up (TMEM,
+// first gathers) and epilogue run under the other's tiles.
 //   warps 0-3   epilogue: TMEM -> bf16 -> dQ[q, head, d]; lane = head, so a thread stores whole 64-byte pieces of
 //               its head's row
 //   warps 4-11  producers: per 64-key tile the part's columns of the kv rows picked by index (16-byte
@@ -1268,39 +1269,45 @@ __global__ void __launch_bounds__(256) smla_dkv_segment_sum_kernel(const int* __
 //               transposed 128x128x16 form reads 8 KB per 64 cycles, which is all the bandwidth there is (measured
 //               ~100 cycles per UMMA instead of 64).  With HP = 64 the upper 64 accumulator rows are computed from
 //               whatever follows the dS tile in shared memory and never read.
+//               (Two issuers taking alternate tiles, handing over through a counter, changed nothing at one CTA
+//               per SM: the kernel waits for its gathers, not for the issuer.)
 // =============================================================================================
 namespace dq {
 constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
-constexpr int kStages = 4;                // 4 x 56 KB: what is in flight bounds this kernel (3 stages: 4 % slower)
-template <int HP> struct Cfg {
-    static constexpr int kKgBytes = 5 * 8192;
+constexpr int kStages = 2;
+template <int HP, int kSplit> struct Cfg {
+    static_assert(kSplit >= 1 && kSplit <= 4, "one UMMA covers the part: N = 64 kSplit <= 256");
+    static constexpr int kKgBytes = kSplit * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
     static constexpr int kStage = kKgBytes + kDsBytes;     // dS right after Kg
     static constexpr int kOffMisc = kStages * kStage;
     // the A operand always spans 128 heads: with HP = 64 its upper half reads 8 KB past the dS tile
     static constexpr int kSmemBytes = kOffMisc + 256 + 1024 + (HP == 64 ? 8192 : 0);
-    static_assert(kSmemBytes <= 232448, "shared memory of one SM");
-    static constexpr int kTmemCols = 512;                  // up to 320 columns of d used
+    static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
+    static constexpr int kTmemCols = 256;                  // up to 256 columns of d; two CTAs share the SM's 512
+    static constexpr int kRowBytes = kSplit * 128 + 16;    // epilogue staging of one head's row
+    static_assert(128 * kRowBytes <= kOffMisc, "the epilogue stages its rows in the pipeline's memory");
 };
 }  // namespace dq
 
 // kNorm (forward, o = S.V): the scratch holds unnormalised E = exp2(logit - max); every head's row is divided by its
 // row sum on the way out, and the CTA of d-part 0 writes lse = max + log2(sum).
 template <int HP, int kSplit, int kTotal, bool kNorm = false>
-__global__ void __launch_bounds__(dq::kThreads, 1)
+__global__ void __launch_bounds__(dq::kThreads, 2)
 smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
-    using C = Cfg<HP>;
-    const int part = blockIdx.x & 1;
-    const int ql = blockIdx.x >> 1;
+    using C = Cfg<HP, kSplit>;
+    constexpr int kParts = (kTotal + kSplit - 1) / kSplit;
+    const int part = blockIdx.x % kParts;
+    const int ql = blockIdx.x / kParts;
     const int qg = p.q0 + ql;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // d-part 0 gathers kv column chunks [0, kSplit), part 1 [kSplit, kTotal): (5, 9) for dQ, (4, 8) for o = S.V
-    const int chunk0 = part ? kSplit : 0;
-    const int n_ch = part ? kTotal - kSplit : kSplit;
+    // d-part i gathers kv column chunks [i kSplit, (i + 1) kSplit): 3 x 3 of 9 for dQ, 2 x 4 of 8 for o = S.V
+    const int chunk0 = part * kSplit;
+    const int n_ch = kTotal - chunk0 < kSplit ? kTotal - chunk0 : kSplit;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1387,25 +1394,24 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         }
     } else if (warp == 12) {
         if (lane == 0) {
-            // N = up to four column chunks (256 d) in one UMMA, the rest (one chunk) in a second
-            const int n1 = (n_ch < 4 ? n_ch : 4) * 64, n2 = (n_ch - 4) * 64;
-            const uint32_t idesc1 = make_idesc_bf16(128, n1, 1, 1);
-            const uint32_t idesc2 = make_idesc_bf16(128, n2 > 0 ? n2 : 64, 1, 1);
+            // N = the part's column chunks (up to 256 d) in one UMMA
+            const uint32_t idesc1 = make_idesc_bf16(128, n_ch * 64, 1, 1);
+            // A = dS^T: [HP/8 head blocks][64 keys][8 heads], 8-key groups 128 B apart, head blocks 1 KB apart.
+            // Descriptors: the fixed fields once, the address (16-byte units, the low 14 bits) added per UMMA.
+            const uint64_t a_hi = make_smem_desc(0, 128, 1024, kSwizzleNone) & 0xFFFFFFFF00000000ull;
+            const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc(0, 128, 1024, kSwizzleNone)) + ((s_base + C::kKgBytes) >> 4);
+            const uint64_t b_hi = make_smem_desc(0, 8192, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
+            const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(0, 8192, 1024, kSwizzle128)) + (s_base >> 4);
             for (int tile = 0; tile < n_tiles; ++tile) {
                 const int s = tile % kStages;
-                mbar_wait(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
+                mbar_spin(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
                 fence_proxy_async_smem();
                 tc_fence_after_sync();
-                const uint32_t kg = s_base + s * C::kStage;
-                const uint32_t ds = kg + C::kKgBytes;
+                const uint32_t a_lo = a_lo0 + s * (C::kStage >> 4), b_lo = b_lo0 + s * (C::kStage >> 4);
 #pragma unroll
                 for (int ks = 0; ks < kTileKeys / 16; ++ks) {
-                    // A = dS^T: [HP/8 head blocks][64 keys][8 heads], 8-key groups 128 B apart, head blocks 1 KB apart
-                    const uint64_t a = make_smem_desc(ds + ks * 256, 128, 1024, kSwizzleNone);
-                    umma_ss(tmem, a, make_smem_desc(kg + ks * 2048, 8192, 1024, kSwizzle128), idesc1, (tile | ks) != 0);
-                    if (n2 > 0)
-                        umma_ss(tmem + 256, a, make_smem_desc(kg + 4 * 8192 + ks * 2048, 8192, 1024, kSwizzle128), idesc2,
-                                (tile | ks) != 0);
+                    const uint64_t a = a_hi | (a_lo + ks * (256 >> 4));
+                    umma_ss(tmem, a, b_hi | (b_lo + ks * (2048 >> 4)), idesc1, (tile | ks) != 0);
                 }
                 umma_commit(bar_empty + 8 * s);
             }
@@ -1424,7 +1430,7 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         // spread over all banks) and sends it off as one bulk copy: whole cache lines instead of 32 scattered
         // 16-byte pieces per store instruction.
         constexpr int kPitch = kTotal * 64;      // 576 for dQ, 512 for o
-        constexpr int kRowBytes = 5 * 128 + 16;  // up to five column chunks per part
+        constexpr int kRowBytes = C::kRowBytes;
         const int head = quarter * 32 + lane;
         const uint32_t row_s = s_base + head * kRowBytes;
         float inv = 1.f;
@@ -1441,17 +1447,17 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
         if (quarter * 32 < p.h_q) {               // warp-uniform: heads are padded to a multiple of 8 only
             const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-            for (int cg = 0; cg < n_ch * 2; ++cg) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + cg * 32, r);
+            for (int cg = 0; cg < n_ch * 4; ++cg) {   // 16 columns at a time: two CTAs per SM leave 64 registers a thread
+                uint32_t r[16];
+                tmem_ld_32x16(taddr + cg * 16, r);
                 tmem_ld_wait();
                 if constexpr (kNorm) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * inv);
+                    for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * inv);
                 }
 #pragma unroll
-                for (int v = 0; v < 4; ++v)
-                    st_shared_v4(row_s + cg * 64 + v * 16,
+                for (int v = 0; v < 2; ++v)
+                    st_shared_v4(row_s + cg * 32 + v * 16,
                                  pack_bf16x2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1])),
                                  pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
                                  pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
