@@ -46,7 +46,7 @@ struct KParams {
     __nv_bfloat16* dQ;        // [s_q, h_q, 576]
     // forward only
     int* m_ord;               // [s_q, h_q] row maximum of the raw logits Q.K, as order-preserving integers
-    unsigned long long* l_fix;// [s_q, h_q] row sum of exp2(logit - max) in 2^-24 fixed point
+    unsigned long long* l_fix;// [s_q, h_q] row sum of exp2(logit - max) in 2^-22 fixed point
     float* lse_out;           // [s_q, h_q]
     float lse_out_mult;       // 1 (base 2) or ln 2 (natural log)
     // dq-style kernel: where the result goes (dQ with pitch 576, or o with pitch 512)
@@ -114,7 +114,7 @@ __device__ __forceinline__ float ordered_to_float(int o) {
     return __int_as_float(o ^ ((o >> 31) & 0x7fffffff));
 }
 constexpr int kOrderedNegInf = static_cast<int>(0xff800000u ^ 0x7fffffffu);   // float_to_ordered(-inf)
-constexpr float kFixScale = 16777216.f;                                          // 2^24
+constexpr float kFixScale = 4194304.f;                                           // 2^22
 
 // =============================================================================================
 // Delta = rowsum(O * dO).  One warp per (query, head) row of 512 bf16; each lane reads 2 x 16 B
@@ -546,7 +546,7 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 // the UMMAs of an accumulator enter the pipe in chunk order and the result is reproducible bit for bit; the streams
 // are independent of each other.
 // kMode 1: row maxima only (atomicMax per head at the end of a query); kMode 2: E = exp2(logit - max) as bf16 into the
-// scratch (the backward's S layout) and the row sums in 2^-24 fixed point.
+// scratch (the backward's S layout) and the row sums in 2^-22 fixed point.
 // =============================================================================================
 namespace fl {
 constexpr int kProducerThreads = 128;
@@ -816,6 +816,7 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                     const size_t off = static_cast<size_t>(p.scr0 + ql) * p.topk_pad * HP + scratch_offset(key, g * NH, p.topk_pad);
                     __nv_bfloat16* s_out = p.s_scr + off;
                     const uint32_t vmask = valid ? 0xFFFFFFFFu : 0u;
+                    const uint32_t fxmask = valid ? 0x007FFFFFu : 0u;
 #pragma unroll 1
                     for (int c0 = 0; c0 < NH; c0 += 16) {
                         uint32_t pv[16];
@@ -835,9 +836,12 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                                 // E <= 1 (+ one rounding): the same logits produced the maximum in the first pass
                                 const float ex = ex2_approx(fmaf(__uint_as_float(pv[c]), p.scale_log2e, -lv[e]));
                                 sv[e] = ex;
-                                // row sums in 2^-24 fixed point: integer warp reductions and integer atomics add in
-                                // any order to the same result, and 2048 terms lose at most 2^-13 of a sum >= 1
-                                const unsigned fx = valid ? __float2uint_rz(ex * kFixScale) : 0u;
+                                // Row sums in 2^-22 fixed point: integer warp reductions and integer atomics add in
+                                // any order to the same result.  E + 2.0f lies in [2, 4), where one unit of the mantissa
+                                // is 2^-22: the low 23 bits of the sum's bit pattern are E in fixed point, rounded to
+                                // nearest, without a conversion instruction (conversions, exponentials and warp
+                                // reductions share one quarter-rate pipe).  2048 terms lose at most 2^-12 of a sum >= 1.
+                                const unsigned fx = __float_as_uint(ex + 2.0f) & fxmask;
                                 const unsigned r = redux_add_u32(fx);
                                 if (lane == ((c0 + c) & 31)) mine = r;
                             }
