@@ -496,6 +496,20 @@ def run_ours(args):
         if per_q is not None and w.h_q == 128 and w.topk == 2048:
             roofline["traffic"] = per_q * seqs[0]["q"].shape[0]
             roofline["traffic_source"] = TRAFFIC_SOURCE[dom] + " (296-query ncu capture, scaled by the number of queries)"
+        # What bounds the dKV kernel is not the tensor pipe but the rate at which the chip takes fp32 reductions: every
+        # (query, slot) adds 576 floats to a kv row.  The ceiling is measured here, on this GPU, with the same instruction
+        # form on random rows of a dKV-sized buffer.
+        if dom == "dkv" and rank == 0:
+            try:
+                ceiling = op.reduction_rate_gbs(w.s_kv, dev)
+                red_bytes = float(seqs[0]["q"].shape[0]) * w.topk * 576 * 4
+                red_gbs = red_bytes / (mm[dom]["ms"] * 1e-3) / 1e9
+                roofline["reduction"] = {"bytes_per_launch": red_bytes, "achieved_gbs": red_gbs, "ceiling_gbs": ceiling,
+                                         "frac": red_gbs / ceiling,
+                                         "how": "ceiling: smla_reduction_rate_probe, red.global.add.f32 on random rows of a "
+                                                "[s_kv, 576] fp32 buffer from all SMs, CUDA events, best of 3"}
+            except Exception as e:      # a measurement aid must not take the line down
+                roofline["reduction"] = {"error": str(e)[:200]}
         # the whole step against the same peak, and where its time goes in SM cycles
         step_tf = flops / (ms * 1e-3) / 1e12
         roofline["step"] = {"achieved_per_gpu": step_tf / world, "frac": step_tf / world / peak}

@@ -230,6 +230,13 @@ int smla_dkv_multimem_reduce(void* multicast_partial, int32_t world, int32_t ran
  * around a timed region give the average SM clock inside it: delta cycles / delta ns per SM. */
 int smla_clock_probe(unsigned long long* out, int n_sm, void* stream);
 
+/* Measurement aid (no counterpart in the reference): n_ctas blocks of 256 threads add 1.0f to every element of
+ * rows_per_cta rows each, picked at random among dst's n_rows rows of row_floats floats, with the instruction form the
+ * dKV scatter uses (red.global.add.f32, a warp per row, 128 consecutive bytes per instruction).  Timed by the caller,
+ * n_ctas * rows_per_cta * row_floats * 4 bytes / time is the rate at which this GPU takes fp32 reductions: the ceiling
+ * the dKV kernel is measured against. */
+int smla_reduction_rate_probe(float* dst, int32_t n_rows, int32_t row_floats, int32_t rows_per_cta, int32_t n_ctas, void* stream);
+
 /* Number of kernels (own kernels, memset excluded) the last smla_bwd_run_stages on this thread launched. */
 int smla_bwd_last_launch_count(void);
 

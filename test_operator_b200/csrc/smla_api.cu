@@ -890,7 +890,25 @@ __global__ void clock_probe_kernel(unsigned long long* out, int n_sm) {
         out[2 * smid + 1] = t;
     }
 }
+// fp32 reductions the way the dkv kernel issues them (one red.global.add.f32 per lane, 32 lanes = 128 consecutive bytes)
+// on rows picked at random: a warp per row, rows_per_cta rows per block.
+__global__ void reduction_rate_probe_kernel(float* dst, uint32_t n_rows, int row_floats, int rows_per_cta) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int r = warp; r < rows_per_cta; r += n_warps) {
+        uint32_t h = blockIdx.x * 1315423911u + static_cast<uint32_t>(r) * 2654435761u + 12345u;
+        h ^= h >> 16; h *= 0x7feb352du; h ^= h >> 15; h *= 0x846ca68bu; h ^= h >> 16;
+        float* g = dst + static_cast<size_t>(h % n_rows) * row_floats;
+        for (int v = lane; v < row_floats; v += 32) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(g + v), "f"(1.f) : "memory");
+    }
+}
 }  // namespace
+
+int smla_reduction_rate_probe(float* dst, int32_t n_rows, int32_t row_floats, int32_t rows_per_cta, int32_t n_ctas, void* stream) {
+    if (!dst || n_rows <= 0 || row_floats <= 0 || rows_per_cta <= 0 || n_ctas <= 0) return SMLA_ERR_BAD_ARG;
+    reduction_rate_probe_kernel<<<n_ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dst, static_cast<uint32_t>(n_rows), row_floats,
+                                                                                          rows_per_cta);
+    return cudaGetLastError() == cudaSuccess ? SMLA_OK : SMLA_ERR_LAUNCH;
+}
 
 int smla_clock_probe(unsigned long long* out, int n_sm, void* stream) {
     if (!out || n_sm <= 0) return SMLA_ERR_BAD_ARG;

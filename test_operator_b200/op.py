@@ -148,6 +148,9 @@ def load_library() -> ctypes.CDLL:
                                                  ctypes.c_int32, ctypes.c_void_p]
         lib.smla_clock_probe.restype = ctypes.c_int
         lib.smla_clock_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.smla_reduction_rate_probe.restype = ctypes.c_int
+        lib.smla_reduction_rate_probe.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                                  ctypes.c_void_p]
         lib.smla_bwd_status_string = lib.smla_status_string
         lib.smla_status_string.restype = ctypes.c_char_p
         lib.smla_status_string.argtypes = [ctypes.c_int]
@@ -630,6 +633,26 @@ class SMClock:
             return None
         d = (b[ok] - a[ok]).double()
         return float((d[:, 0] / d[:, 1] * 1e3).mean().item())
+
+
+def reduction_rate_gbs(s_kv: int, device, row_floats: int = 576, rows_per_cta: int = 8192, reps: int = 3) -> float:
+    """GB/s at which this GPU takes fp32 reductions on random rows of a [s_kv, row_floats] buffer (one dKV), issued the
+    way the dKV kernel issues them, one block per SM: the ceiling that kernel is measured against.  Best of `reps`."""
+    lib = load_library()
+    n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+    buf = torch.zeros(s_kv, row_floats, dtype=torch.float32, device=device)
+    st = torch.cuda.current_stream().cuda_stream
+    best = 0.0
+    for i in range(reps + 1):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _raise_status(lib, lib.smla_reduction_rate_probe(buf.data_ptr(), s_kv, row_floats, rows_per_cta, n_sm, st),
+                      "smla_reduction_rate_probe")
+        b.record()
+        b.synchronize()
+        if i:       # the first launch warms up
+            best = max(best, n_sm * rows_per_cta * row_floats * 4 / (a.elapsed_time(b) * 1e-3) / 1e9)
+    return best
 
 
 def last_launch_count() -> int:
