@@ -10,9 +10,9 @@
 //              fp32 reduction per (key, 32 consecutive d) straight from TMEM registers
 //   dq         dQ[head, d] = dS^T K_g (tcgen05, heads on the M axis, d on N) accumulated over all keys
 //
-// The forward (o, lse for the same indices) reuses two of them: the recompute kernel with B = Q only, once to find
-// every row's maximum logit and once to write E = exp2(logit - max) and the row sums, and the dq kernel on the V
-// columns, dividing by the sums on the way out.
+// The forward (o, lse for the same indices) has a logits kernel of its own (one CTA per query with Q of all heads
+// resident), run once to find every row's maximum logit and once to write E = exp2(logit - max) and the row sums, and
+// reuses the dq kernel on the V columns, dividing by the sums on the way out.
 //
 // Heads are padded to HP = 64 or 128, so h_q = 16 / 64 / 128 use the same code.  Gathered kv rows and
 // Q / dO are held as 128-byte-swizzled [rows x 64 bf16] chunks (kv rows by 16-byte cp.async, Q / dO by
