@@ -516,8 +516,8 @@ def run_ours(args):
         if step_mhz and all("mcycles" in v for v in kernels.values()) and world == 1 and len(seqs) == 1:
             kc = sum(v["mcycles"] for v in kernels.values())
             roofline["step"].update({"sm_mhz": step_mhz, "mcycles": ms * step_mhz * 1e-3, "kernels_alone_mcycles": kc,
-                                     "note": "mcycles = ms x mean SM MHz from the SMs' cycle counters; with the dKV kernel "
-                                             "overlapped the step takes fewer cycles than its kernels timed one by one"})
+                                     "note": "mcycles = ms x mean SM MHz from the SMs' cycle counters: the step against the "
+                                             "sum of its kernels timed one by one, in cycles (the clock differs)"})
 
     # ---- the same step back to back for about a second (one GPU): the power cap then sets the clock, so this is the
     # figure to hold against the sustained measured peak, as the short timed region is to the burst peak ---------
@@ -689,7 +689,9 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic",
             "config": _config(wname, w, args.s_q,
                               ("query+reduce_scatter" if query_sharded else "batch") if world > 1 else "none"),
-            "stages": stages, "schedule": dict(zip(("chunks", "dkv_pairs"), op.get_schedule())),
+            "stages": stages, "schedule": dict(zip(("chunks", "dkv_pairs"), op.get_schedule()),
+                                                note="chunks -1: chosen from the head count (64 heads: two overlapped parts; "
+                                                     "128: the kernels one after the other)"),
             "clocks": clocks, "gpu_launches": n_launch, "kernels": kernels,
             "device_status": "ok" if not bad_status else "TIMEOUT in: " + "; ".join(bad_status),
         }

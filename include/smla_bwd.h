@@ -189,11 +189,12 @@ int smla_bwd_last_device_code(void);
  * chunks >= 2: the queries of a pass are cut into that many parts and the dKV kernel of a part runs on a second
  * stream owned by the library, on `dkv_pairs` 2-SM clusters (0: chosen by the library from the head count), beside
  * the recompute and dQ kernels of the next part: the dKV kernel keeps the load/store path busy and the tensor cores
- * a third of the time, the other two the reverse, and the chip's fp32 reduction rate serves a dKV kernel on half the
- * SMs better than one on all of them.  Default: 2 parts, automatic.  A pass falls back to one-after-the-other when it
- * has too few queries to keep every cluster busy in every part.  The second stream and its events
- * are created by the first call that needs them on a device: make that call before a stream capture begins.
- * Process-wide; the environment variable SMLA_SCHEDULE="chunks,dkv_pairs" sets the initial value. */
+ * a third of the time, the other two the reverse.  chunks = -1 (the default): chosen by the library from the head
+ * count - two overlapped parts up to 64 heads, one after another with 128, which is what measured faster on B200.
+ * A pass falls back to one-after-the-other when it has too few queries to keep every cluster busy in every part.
+ * The second stream and its events are created by the first call that needs them on a device: make that call before a
+ * stream capture begins.  Process-wide; the environment variable SMLA_SCHEDULE="chunks,dkv_pairs" sets the initial
+ * value.  smla_bwd_get_schedule returns what was set (-1 for automatic), not what a head count resolves to. */
 int smla_bwd_set_schedule(int chunks, int dkv_pairs);
 void smla_bwd_get_schedule(int* chunks, int* dkv_pairs);
 

@@ -36,19 +36,19 @@ thread_local int g_last_device_code = 0;
 //   chip's fp32 reduction rate, not by its SMs, so it loses little on fewer SMs, and the SMs it leaves do the
 //   tensor-core work of the other two kernels meanwhile.
 constexpr int kMaxChunks = 16;
-std::atomic<int> g_sched_chunks{-1};      // -1: not yet read from the environment
+std::atomic<int> g_sched_chunks{-2};      // -2: not yet read from the environment; -1: chosen per head count
 std::atomic<int> g_sched_dkv_pairs{0};
-constexpr int kDefaultChunks = 2;         // measured on B200: two parts beat three and more (each launch has its own tail)
+constexpr int kDefaultChunks = -1;        // chosen from the head count, see auto_chunks
 constexpr int kDefaultDkvPairs = 0;       // 0: chosen from the head count, see auto_dkv_pairs
 std::atomic<long long> g_wait_limit{smla::kWaitLimitCycles};
 
 void schedule(int* chunks, int* dkv_pairs) {
     int c = g_sched_chunks.load();
-    if (c < 0) {
+    if (c < -1) {
         int cc = kDefaultChunks, dp = kDefaultDkvPairs;
         if (const char* e = std::getenv("SMLA_SCHEDULE")) {      // "chunks,dkv_pairs"
             int a = 0, b = 0;
-            if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 0 && a <= kMaxChunks && b >= 0) {
+            if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= -1 && a != 1 && a <= kMaxChunks && b >= 0) {
                 cc = a;
                 dp = b;
             }
@@ -64,6 +64,12 @@ void schedule(int* chunks, int* dkv_pairs) {
 // Clusters for the dkv kernel when the caller leaves the choice to the library: its share of the three kernels'
 // time, measured with each kernel alone on a whole B200 (top-k 2048; dkv 3.8 ms at either head count, recompute +
 // dq 3.4 ms at 128 heads and 2.65 ms at 64).  The step time is flat within +-3 clusters of these.
+// Measured on B200, alternating the schedules on one GPU: with 64 heads two overlapped parts beat one kernel after the
+// other by 4 % (5.89 against 6.16 ms; three parts and more lose to two, each launch has its own tail); with 128 heads the
+// kernels one after the other are 2.5 % faster than any overlapped form (7.39 against 7.60 ms, 8.64 against 8.85 ms over
+// a second of steps): there the recompute and dQ kernels want all of the SMs more than the dKV kernel minds having them.
+int auto_chunks(int h_pad) { return h_pad > 64 ? 0 : 2; }
+
 int auto_dkv_pairs(int h_pad, int resident) {
     const double share = h_pad > 64 ? 0.50 : 0.58;
     int n = static_cast<int>(resident * share + 0.5);
@@ -330,6 +336,7 @@ int launch_chain(const smla_bwd_params* p, const Plan& pl, uint8_t* ws, cudaStre
 
     int chunks = 0, dkv_pairs = 0;
     schedule(&chunks, &dkv_pairs);
+    if (chunks < 0) chunks = auto_chunks(HP);
     const int all = SMLA_STAGE_RECOMPUTE | SMLA_STAGE_DKV | SMLA_STAGE_DQ;
     if (dkv_pairs <= 0) dkv_pairs = auto_dkv_pairs(HP, pairs_d < pairs_r ? pairs_d : pairs_r);
     if (!allow_overlap || det || (stages & all) != all || dkv_pairs >= pairs_d || dkv_pairs >= pairs_r) chunks = 0;
@@ -592,7 +599,7 @@ int smla_bwd_workspace_init(void* workspace, void* stream) {
 }
 
 int smla_bwd_set_schedule(int chunks, int dkv_pairs) {
-    if (chunks < 0 || chunks > kMaxChunks || chunks == 1 || dkv_pairs < 0) return SMLA_ERR_BAD_ARG;   // dkv_pairs 0: automatic
+    if (chunks < -1 || chunks > kMaxChunks || chunks == 1 || dkv_pairs < 0) return SMLA_ERR_BAD_ARG;   // -1 / 0 pairs: automatic
     g_sched_dkv_pairs.store(dkv_pairs);
     g_sched_chunks.store(chunks);
     return SMLA_OK;

@@ -581,7 +581,8 @@ def last_device_code() -> int:
 
 
 def set_schedule(chunks: int, dkv_pairs: int) -> None:
-    """How one pass of the backward is scheduled (`smla_bwd_set_schedule`): 0 chunks = one kernel after the other."""
+    """How one pass of the backward is scheduled (`smla_bwd_set_schedule`): 0 chunks = one kernel after the other,
+    -1 = chosen by the library from the head count (the default)."""
     lib = load_library()
     _raise_status(lib, lib.smla_bwd_set_schedule(int(chunks), int(dkv_pairs)), "smla_bwd_set_schedule")
 

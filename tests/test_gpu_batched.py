@@ -76,8 +76,13 @@ def test_batched_large_enough_for_the_overlapped_schedule():
     w = Workload("bl", 1, 400, 640, 128, 256, "uniform", invalid_frac=0.1)
     seqs = [make_sequence(w, device=DEV, seed=61 + b) for b in range(3)]
     stacked = {k: torch.stack([s[k] for s in seqs]) for k in KEYS}
-    dq, dkv = op.mla_bwd_batched(*[stacked[k] for k in KEYS], q_start_index_s=300, check_device_status=True)
-    assert op.last_launch_count() == 1 + 3 * max(1, op.get_schedule()[0])
+    before = op.get_schedule()
+    op.set_schedule(2, 0)
+    try:
+        dq, dkv = op.mla_bwd_batched(*[stacked[k] for k in KEYS], q_start_index_s=300, check_device_status=True)
+        assert op.last_launch_count() == 1 + 3 * 2
+    finally:
+        op.set_schedule(*before)
     for b, s in enumerate(seqs):
         dq_ref, dkv_ref = sparse_mla_bwd_ref(*[s[k] for k in KEYS], q_start_index_s=300, chunk_s=16)
         assert_backward_close(dq[b], dkv[b], dq_ref, dkv_ref, f"sequence {b}")

@@ -42,12 +42,38 @@ def test_overlapped_schedule_matches_sequential_and_oracle(chunks, dkv_pairs):
     assert_backward_close(dq1, dkv1, dq_ref, dkv_ref, "overlapped")
 
 
-def test_default_schedule_overlaps_and_replays_from_a_cuda_graph():
-    """The library's default is the overlapped schedule; its second stream forks from and joins the caller's stream, so
-    a capture of the caller's stream takes the whole call (the first call, which creates that stream, came before)."""
+def test_overlapped_schedule_replays_from_a_cuda_graph():
+    """The overlapped schedule's second stream forks from and joins the caller's stream, so a capture of the caller's
+    stream takes the whole call (the first call, which creates that stream, came before)."""
     from test_operator_b200 import op
-    assert op.get_schedule()[0] >= 2
-    w = Workload("sched_graph", 1, 1400, 2048, 128, 256, "uniform", invalid_frac=0.1)
+    before = op.get_schedule()
+    op.set_schedule(2, 0)
+    try:
+        _graph_replay_case(op, 128)
+    finally:
+        op.set_schedule(*before)
+
+
+def test_default_schedule_follows_the_head_count():
+    """Automatic (-1): two overlapped parts with 64 heads, the kernels one after the other with 128."""
+    from test_operator_b200 import op
+    before = op.get_schedule()
+    op.set_schedule(-1, 0)
+    try:
+        for h_q, launches in ((64, 1 + 3 * 2), (128, 1 + 3)):
+            w = Workload("sched_auto", 1, 1400, 2048, h_q, 256, "uniform", invalid_frac=0.1)
+            s = make_sequence(w, device=DEV, seed=39)
+            args = [s[k] for k in KEYS]
+            dq, dkv = op.mla_bwd(*args, q_start_index_s=None, check_device_status=True)
+            assert op.last_launch_count() == launches
+            dq_ref, dkv_ref = sparse_mla_bwd_ref(*args, q_start_index_s=None, chunk_s=16)
+            assert_backward_close(dq, dkv, dq_ref, dkv_ref, f"automatic schedule, {h_q} heads")
+    finally:
+        op.set_schedule(*before)
+
+
+def _graph_replay_case(op, h_q):
+    w = Workload("sched_graph", 1, 1400, 2048, h_q, 256, "uniform", invalid_frac=0.1)
     s = make_sequence(w, device=DEV, seed=38)
     args = [s[k] for k in KEYS]
     ws = op.workspace_for(s["q"], s["kv"], s["indices"])

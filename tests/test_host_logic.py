@@ -75,9 +75,9 @@ def test_new_entry_points_refuse_bad_arguments_without_a_gpu():
     p = op._Params(0, 0, 0, 0, 0, 0, 0, 0, 64, 256, 16, 64, 0.0, 0, 1)
     assert lib.smla_bwd_staging_bytes_per_query(ctypes.byref(p)) == 256 * 576 * 4       # top-k padded to 256 slots
     assert lib.smla_bwd_run_deterministic(ctypes.byref(p), None, None, 0, None, 31) == 1
-    assert lib.smla_bwd_set_schedule(1, 0) == 1 and lib.smla_bwd_set_schedule(-1, 0) == 1
+    assert lib.smla_bwd_set_schedule(1, 0) == 1 and lib.smla_bwd_set_schedule(-2, 0) == 1
     c, d = op.get_schedule()
-    assert c == 2 and d == 0                                                         # the library's default
+    assert c == -1 and d == 0                                                        # the library's default: automatic
     assert lib.smla_dkv_pull_reduce(None, 2, 0, 64, None, 0, None) == 1
     assert lib.smla_dkv_multimem_reduce(None, 2, 0, 64, None, 0, None) == 1
     assert lib.smla_selftest_wait_timeout(None, 0, 1000, None, None) == 1
