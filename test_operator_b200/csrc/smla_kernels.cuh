@@ -526,9 +526,9 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 // =============================================================================================
 // forward logits, one CTA per query (persistent, queries round-robin), single-CTA UMMAs.
 //
-// A pair UMMA (cta_group::2, M 256) occupies the issuing side for ~163 cycles whatever its N, a single-CTA UMMA of
-// M 128 x N 128 for its 64 cycles of math (measured, standalone).  With B = Q only there is no dO to share the
-// shared memory with, so a CTA can hold Q of ALL heads (9 x [HP heads x 64 col] = 144 KB at 128 heads) and work alone:
+// With B = Q only there is no dO to share the shared memory with, so a CTA can hold Q of ALL heads
+// (9 x [HP heads x 64 col] = 144 KB at 128 heads) and work alone, with UMMAs of M 128 x N = HP that the tensor pipe takes
+// every 64 cycles (51 at N = 64; probes/umma_issue_probe.cu) and no signalling between CTAs:
 //   A  the CTA's 128 gathered keys of a tile, chunk by chunk through a ring of [128 keys x 64 col] chunks
 //   B  Q_j of all heads;  D  [128 keys] x [HP heads] in TMEM, four buffers
 //   warps 0-7   row statistics / exponentials on the tile: warp w -> TMEM lane quarter w % 4, head half w / 4
