@@ -413,7 +413,7 @@ void fwd_layout(const smla_fwd_params* p, FwdPlan* pl, size_t qc) {
 bool make_fwd_plan(const smla_fwd_params* p, size_t budget, FwdPlan* pl) {
     if (!check_fwd_params(p)) return false;
     pl->h_pad = p->h_q <= 64 ? 64 : 128;
-    pl->topk_pad = (p->topk + 255) / 256 * 256;
+    pl->topk_pad = (p->topk + 511) / 512 * 512;   // the logits kernel walks pairs of 256-key tiles
     const size_t unit = size_t(pl->topk_pad) * pl->h_pad * 2;
     if (budget == 0) budget = kDefaultBudget;
     fwd_layout(p, pl, 1);
@@ -444,14 +444,14 @@ template <int HP>
 int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, cudaStream_t st) {
     using namespace smla;
     __nv_bfloat16* s_scr = reinterpret_cast<__nv_bfloat16*>(ws + pl.s_off);
-    CUtensorMap tm_qhp, tm_s;
+    CUtensorMap tm_qnh, tm_s;
     const uint64_t qrows = uint64_t(p->s_q) * p->h_q;
     bool ok = true;
-    ok &= make_map_2d(&tm_qhp, p->q, kDQK, qrows, kDQK * 2, 64, HP);
+    ok &= make_map_2d(&tm_qnh, p->q, kDQK, qrows, kDQK * 2, 64, HP / 2);
     ok &= make_map_scratch(&tm_s, s_scr, uint64_t(pl.q_chunk), pl.topk_pad, HP, 64);
     if (!ok) return SMLA_ERR_LAUNCH;
-    bool attr_ok = set_smem(smla_fwd_logits_kernel<HP, 1>, fl::Cfg<HP>::kSmemBytes);
-    attr_ok &= set_smem(smla_fwd_logits_kernel<HP, 2>, fl::Cfg<HP>::kSmemBytes);
+    bool attr_ok = set_smem(smla_fwd_logits_pair_kernel<HP, 1>, fp::Cfg<HP>::kSmemBytes);
+    attr_ok &= set_smem(smla_fwd_logits_pair_kernel<HP, 2>, fp::Cfg<HP>::kSmemBytes);
     // o = E.V: the two d-parts gather V column chunks [0,4) and [4,8)
     attr_ok &= set_smem(smla_dq_kernel<HP, kVChunks / 2, kVChunks, true>, dq::Cfg<HP, kVChunks / 2>::kSmemBytes);
     if (!attr_ok) return SMLA_ERR_LAUNCH;
@@ -481,16 +481,16 @@ int launch_fwd_chain(const smla_fwd_params* p, const FwdPlan& pl, uint8_t* ws, c
     const int n_rows = p->s_q * p->h_q;
     smla_fwd_stats_init_kernel<<<(n_rows + 255) / 256, 256, 0, st>>>(kp.m_ord, kp.l_fix, n_rows);
     ++g_last_launches;
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-        return SMLA_ERR_LAUNCH;
+    const int pairs_1 = resident_pairs(smla_fwd_logits_pair_kernel<HP, 1>, fp::kThreads, fp::Cfg<HP>::kSmemBytes);
+    const int pairs_2 = resident_pairs(smla_fwd_logits_pair_kernel<HP, 2>, fp::kThreads, fp::Cfg<HP>::kSmemBytes);
+    if (pairs_1 <= 0 || pairs_2 <= 0) return SMLA_ERR_LAUNCH;
     for (int q0 = 0; q0 < p->s_q; q0 += pl.q_chunk) {
         const int nq = (p->s_q - q0 < pl.q_chunk) ? p->s_q - q0 : pl.q_chunk;
         kp.q0 = q0;
         kp.nq = nq;
-        const int grid = nq < sms ? nq : sms;       // one persistent CTA per SM (each takes the whole shared memory)
-        smla_fwd_logits_kernel<HP, 1><<<grid, fl::kThreads, fl::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, kp);
-        smla_fwd_logits_kernel<HP, 2><<<grid, fl::kThreads, fl::Cfg<HP>::kSmemBytes, st>>>(tm_qhp, kp);
+        // persistent 2-CTA clusters, one per SM pair (each CTA takes the whole shared memory of its SM)
+        smla_fwd_logits_pair_kernel<HP, 1><<<2 * (nq < pairs_1 ? nq : pairs_1), fp::kThreads, fp::Cfg<HP>::kSmemBytes, st>>>(tm_qnh, kp);
+        smla_fwd_logits_pair_kernel<HP, 2><<<2 * (nq < pairs_2 ? nq : pairs_2), fp::kThreads, fp::Cfg<HP>::kSmemBytes, st>>>(tm_qnh, kp);
         smla_dq_kernel<HP, kVChunks / 2, kVChunks, true><<<nq * 2, dq::kThreads, dq::Cfg<HP, kVChunks / 2>::kSmemBytes, st>>>(tm_s, kp);
         g_last_launches += 3;
     }

@@ -10,8 +10,8 @@
 //              fp32 reduction per (key, 32 consecutive d) straight from TMEM registers
 //   dq         dQ[head, d] = dS^T K_g (tcgen05, heads on the M axis, d on N) accumulated over all keys
 //
-// The forward (o, lse for the same indices) has a logits kernel of its own (one CTA per query with Q of all heads
-// resident), run once to find every row's maximum logit and once to write E = exp2(logit - max) and the row sums, and
+// The forward (o, lse for the same indices) has a logits kernel of its own (2-CTA pairs with Q resident and two tiles
+// in flight), run once to find every row's maximum logit and once to write E = exp2(logit - max) and the row sums, and
 // reuses the dq kernel on the V columns, dividing by the sums on the way out.
 //
 // Heads are padded to HP = 64 or 128, so h_q = 16 / 64 / 128 use the same code.  Gathered kv rows and
@@ -524,38 +524,48 @@ smla_recompute_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 }
 
 // =============================================================================================
-// forward logits, one CTA per query (persistent, queries round-robin), single-CTA UMMAs.
+// forward logits as persistent 2-CTA clusters: one pair per query (queries round-robin).
 //
-// With B = Q only there is no dO to share the shared memory with, so a CTA can hold Q of ALL heads
-// (9 x [HP heads x 64 col] = 144 KB at 128 heads) and work alone, with UMMAs of M 128 x N = HP that the tensor pipe takes
-// every 64 cycles (51 at N = 64; probes/umma_issue_probe.cu) and no signalling between CTAs:
-//   A  the CTA's 128 gathered keys of a tile, chunk by chunk through a ring of [128 keys x 64 col] chunks
-//   B  Q_j of all heads;  D  [128 keys] x [HP heads] in TMEM, four buffers
-//   warps 0-7   row statistics / exponentials on the tile: warp w -> TMEM lane quarter w % 4, head half w / 4
-//   warps 8-11  gather producers (cp.async 16 B, swizzled)
-//   warps 12-15 the four UMMA issuers
-//   warp 16     TMA of the query's Q chunks
-// Two tiles are in flight at a time: the ring carries their chunks alternately (tile 2t chunk j, tile 2t+1 chunk j,
-// tile 2t chunk j+1, ...): the even ring positions are the chunk stream of the even tiles, the odd positions that of the
-// odd tiles, and each stream accumulates into buffers of its own.  With two pairs of buffers the statistics warps read
-// one pair of tiles while the next pair accumulates.
-// A thread that issues UMMAs executes everything slowly (measured in this kernel: ~370 cycles for the four UMMAs of a
-// chunk, ~240 for its commits, ~200 for advancing a handful of counters, ~1050 per chunk in all, against 256 cycles of
-// tensor-pipe time), so a stream is shared by two issuers that take alternate chunks: four threads, each with
-// 4 x 256 cycles per chunk of its own.  The two issuers of a stream hand over through a counter in shared memory, so
-// the UMMAs of an accumulator enter the pipe in chunk order and the result is reproducible bit for bit; the streams
-// are independent of each other.
+// With B = Q only there is no dO to share the shared memory with: a CTA holds Q of HALF the heads (9 chunks of
+// [HP/2 heads x 64 col], 72 KB at 128 heads), which leaves nine ring slots for the gathered keys.
+//   cta_group::2 UMMAs of M = 256 keys (128 gathered by each CTA) x N = HP heads (HP/2 supplied by each CTA) x K = 16;
+//   D  this CTA's [128 keys] x [HP heads] in TMEM, four buffers of HP columns
+//   warps 0-7   row statistics / exponentials on the CTA's own keys: warp w -> TMEM lane quarter w % 4, head half w / 4
+//   warps 8-15  gather producers (cp.async 16 B, swizzled), one group of four warps per tile stream
+//   warps 16-19 even CTA: the four UMMA issuers for the pair; odd CTA: warp 16 forwards "my slot is full"
+//   warp 20     TMA of the CTA's Q chunks
+// Two 256-key tiles are in flight at a time, as two independent streams (the even tiles and the odd tiles): each stream
+// has its own producer group, its own ring slots (five and four), its own pair of accumulator buffers (one is read by
+// the statistics warps while the other fills) and two issuers; the streams share only the tensor pipe.  Ring slots of
+// its own matter: a producer group that fills a slot has then itself seen the slot's previous use, so its wait on the
+// phase parity of "slot free" cannot be satisfied by the phase before last (with one ring shared by the two groups a
+// group that ran ahead of the other overwrote a slot in use and arrived twice on one barrier phase).
+// A thread that issues UMMAs executes everything slowly (cycle counters: ~450 cycles for the four UMMAs of a chunk,
+// ~270 for its commits, ~230 for advancing a handful of counters, against 256 cycles of tensor-pipe time), so a stream
+// is shared by two issuers that take alternate chunks and hand over through a counter in shared memory: the UMMAs of an
+// accumulator enter the pipe in chunk order and the result is reproducible bit for bit.
+// Slot-free, chunk-free and accumulator-ready signals are tcgen05.commit arrivals delivered to both CTAs.
 // kMode 1: row maxima only (atomicMax per head at the end of a query); kMode 2: E = exp2(logit - max) as bf16 into the
 // scratch (the backward's S layout) and the row sums in 2^-22 fixed point.
 // =============================================================================================
-namespace fl {
-constexpr int kProducerThreads = 128;
-constexpr int kThreads = 256 + kProducerThreads + 128 + 32;   // statistics, producers, issuers, Q loader
-constexpr int kTileKeys = 128;
+namespace fp {
+constexpr int kProducerWarps = 8;
+constexpr int kProducerThreads = 32 * kProducerWarps;
+constexpr int kRowStep = 2 * kProducerWarps;              // a producer thread copies rows r0 + kRowStep * i of its tile
+constexpr int kRowsPerThread = 128 / kRowStep;
+constexpr int kIssuerWarp = 8 + kProducerWarps;           // the first issuer warp
+constexpr int kIssuersPerStream = 2;
+constexpr int kIssuers = 2 * kIssuersPerStream;
+constexpr int kThreads = 256 + kProducerThreads + 32 * kIssuers + 32;   // statistics, producers, issuers, Q loader
+constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;
 template <int HP> struct Cfg {
-    static constexpr int kBChunk = HP * 128;                       // Q_j of all heads
-    static constexpr int kStages = HP == 128 ? 5 : 9;
+    static constexpr int kBChunk = (HP / 2) * 128;                 // Q_j of this CTA's heads
+    static constexpr int kStages = 9;
+    // every tile stream has ring slots of its own (a slot is then always filled by the same producer group, which has
+    // seen its previous use: waits on a barrier's phase parity cannot be taken for the phase before last)
+    static constexpr int kStages0 = (kStages + 1) / 2;             // stream 0: slots [0, kStages0)
+    static constexpr int kStages1 = kStages / 2;                   // stream 1: slots [kStages0, kStages)
     static constexpr int kOffB = 0;
     static constexpr int kOffRing = kQChunks * kBChunk;
     static constexpr int kOffMisc = kOffRing + kStages * kChunkA;
@@ -563,17 +573,18 @@ template <int HP> struct Cfg {
     static constexpr int kTmemCols = 4 * HP;                       // two pairs of accumulator buffers
     static_assert(kSmemBytes <= 232448, "shared memory of one SM");
 };
-}  // namespace fl
+}  // namespace fp
 
 template <int HP, int kMode>
-__global__ void __launch_bounds__(fl::kThreads, 1)
-smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p) {
-    using namespace fl;
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(fp::kThreads, 1)
+smla_fwd_logits_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p) {
+    using namespace fp;
     using C = Cfg<HP>;
     constexpr int NH = HP / 2;
     constexpr int kStages = C::kStages;
-    const int cta = blockIdx.x;
-    const int n_ctas = gridDim.x;
+    const uint32_t rank = cluster_ctarank();
+    const int cta = blockIdx.x >> 1;         // the pair
+    const int n_ctas = gridDim.x >> 1;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
@@ -592,15 +603,16 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 1024 + 8 * (2 * kStages + 2 * kQChunks + 8));
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t tok = smem_u32(tmem_slot + 2);           // [2] chunks issued so far in each stream: the issuers' hand-over
-    const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [4] one per issuer, used only while winding down after an abort
-    static_assert(8 * (2 * kStages + 2 * kQChunks + 8) + 16 + 32 <= 512, "barrier area");
-    const WaitCtx wc{p.g_err, s_abort, p.wait_limit, 0u};
+    const uint32_t bar_drain = smem_u32(tmem_slot + 4);     // [kIssuers] used only while winding down after an abort
+    static_assert(8 * (2 * kStages + 2 * kQChunks + 8) + 16 + 8 * kIssuers <= 512, "barrier area");
+    const WaitCtx wc{p.g_err, s_abort, p.wait_limit, map_to_cta(smem_u32(tmem_slot + 1), rank ^ 1)};
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
         tmem_slot[2] = tmem_slot[3] = 0;
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(bar_full + 8 * i, kProducerThreads);
+            // the even CTA's "full" also counts one arrival forwarded from the odd CTA
+            mbar_init(bar_full + 8 * i, kProducerThreads / 2 + (rank == 0 ? 1 : 0));   // one producer group per slot
             mbar_init(bar_empty + 8 * i, 1);
         }
         for (int i = 0; i < kQChunks; ++i) {
@@ -609,88 +621,90 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 8);    // eight softmax warps
+            mbar_init(bar_tempty + 8 * i, 16);   // eight statistics warps in each CTA
         }
-        for (int i = 0; i < 4; ++i) mbar_init(bar_drain + 8 * i, 1);
+        for (int i = 0; i < kIssuers; ++i) mbar_init(bar_drain + 8 * i, 1);
         fence_mbar_init();
     }
-    if (warp == 12) {
-        tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
-        tmem_relinquish();
+    if (warp == kIssuerWarp) {
+        tmem_alloc_2cta(smem_u32(tmem_slot), C::kTmemCols);
+        tmem_relinquish_2cta();
     }
     tc_fence_before_sync();
     __syncthreads();
+    cluster_sync_all();          // barriers of both CTAs are initialised before anyone signals across
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const int n_tp = p.topk_pad / (2 * kTileKeys);      // tile pairs; the padded top-k is a multiple of 256
+    const int n_tp = p.topk_pad / (2 * kTileKeys);      // tile pairs; the forward pads the top-k to a multiple of 512
     const int nq = p.nq;
 
-    if (warp >= 8 && warp < 12) {
+    if (warp >= 8 && warp < kIssuerWarp) {
         // ------------------------------------------------------------------ gather producers
-        const int pt = threadIdx.x - 256;   // 0..127
+        // Two groups of kProducerWarps / 2 warps, one per tile stream: group x fills every second ring position, the
+        // chunks of tile 2t + x, so a warp waits and arrives once per two positions and the streams do not hold each
+        // other up.
+        const int grp = (warp - 8) / (kProducerWarps / 2);
+        const int pt = threadIdx.x - 256 - grp * (kProducerThreads / 2);
         const int u = pt & 7;               // 16-byte unit inside a 128-byte chunk row
-        const int r0 = pt >> 3;             // rows r0 + 16 i of the tile's 128 keys
+        const int r0 = pt >> 3;             // rows r0 + kRowStep * i of the CTA's 128 keys
         const uint32_t dst0 = s_base + C::kOffRing + r0 * 128 + ((u ^ (r0 & 7)) << 4);
         const char* kvb = reinterpret_cast<const char*>(p.kv) + u * 16;
         const uint64_t pol_keep = l2_policy_evict_last();
-        // raw index values, loaded one tile pair ahead and turned into kv rows when they are used
+        // raw index values, loaded one tile ahead and turned into kv rows when they are used
         QMeta qm_next = load_qmeta(p, p.q0 + (cta < nq ? cta : 0));
-        int idx_next[2][8];
+        int idx_next[kRowsPerThread];
         auto load_idx = [&](int ql, int tp) {
             if (ql >= nq) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) idx_next[0][i] = idx_next[1][i] = -1;
+                for (int i = 0; i < kRowsPerThread; ++i) idx_next[i] = -1;
                 return;
             }
             if (tp == 0) qm_next = load_qmeta(p, p.q0 + ql);
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int key = (2 * tp + sub) * kTileKeys + r0 + 16 * i;
-                    idx_next[sub][i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
-                }
+            for (int i = 0; i < kRowsPerThread; ++i) {
+                const int key = (2 * tp + grp) * kTileKeys + static_cast<int>(rank) * 128 + r0 + kRowStep * i;
+                idx_next[i] = key < p.topk ? __ldg(p.indices + static_cast<size_t>(p.q0 + ql) * p.topk + key) : -1;
+            }
         };
         load_idx(cta, 0);
-        int s = 0;
+        const int ring0 = grp ? C::kStages0 : 0, ring_n = grp ? C::kStages1 : C::kStages0;
+        int rs = 0;                         // slot of the group's ring
         uint32_t ph = 1;                    // parity that means "slot free" for the current pass over the ring
         for (int ql = cta; ql < nq; ql += n_ctas) {
             for (int tp = 0; tp < n_tp; ++tp) {
-                int row[2][8];              // kv row, or -1: slot out of range, read nothing and land zeros
+                const char* src[kRowsPerThread];
+                uint32_t nb[kRowsPerThread];    // 0: slot out of range, read nothing and land zeros
 #pragma unroll
-                for (int sub = 0; sub < 2; ++sub)
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) row[sub][i] = gather_row(idx_next[sub][i], qm_next, p);
+                for (int i = 0; i < kRowsPerThread; ++i) {
+                    const int row = gather_row(idx_next[i], qm_next, p);
+                    nb[i] = row >= 0 ? 16u : 0u;
+                    src[i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
+                }
                 if (tp + 1 < n_tp) load_idx(ql, tp + 1);
                 else load_idx(ql + n_ctas, 0);
                 for (int j = 0; j < kQChunks; ++j) {
+                    const int s = ring0 + rs;
+                    mbar_wait(bar_empty + 8 * s, ph, wc, kErrFwd + 11, kPollSleepNs);
+                    const uint32_t d = dst0 + s * kChunkA;
 #pragma unroll
-                    for (int sub = 0; sub < 2; ++sub) {
-                        mbar_wait(bar_empty + 8 * s, ph, wc, kErrFwd + 11, kPollSleepNs);
-                        const uint32_t d = dst0 + s * kChunkA;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int r = row[sub][i];
-                            cp_async16_zfill_hint(d + i * 16 * 128, kvb + static_cast<size_t>(r >= 0 ? r : 0) * (kDQK * 2) + j * 128,
-                                                  r >= 0 ? 16u : 0u, pol_keep);
-                        }
-                        cp_async_mbar_arrive_noinc(bar_full + 8 * s);
-                        if (++s == kStages) {
-                            s = 0;
-                            ph ^= 1;
-                        }
+                    for (int i = 0; i < kRowsPerThread; ++i)
+                        cp_async16_zfill_hint(d + i * kRowStep * 128, src[i] + j * 128, nb[i], pol_keep);
+                    cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+                    if (++rs == ring_n) {
+                        rs = 0;
+                        ph ^= 1;
                     }
                 }
             }
         }
-    } else if (warp == 16) {
+    } else if (warp == kIssuerWarp + kIssuers) {
         // ------------------------------------------------------------------ Q chunks of the query (all heads)
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             const uint64_t pol_stream = l2_policy_evict_first();
             uint32_t qpar = 1;              // parity of "chunk free" left by the previous query
             for (int ql = cta; ql < nq; ql += n_ctas, qpar ^= 1) {
-                const int row0 = (p.q0 + ql) * p.h_q;
+                const int row0 = (p.q0 + ql) * p.h_q + NH * static_cast<int>(rank);
                 for (int j = 0; j < kQChunks; ++j) {
                     if (ql != cta) mbar_wait(bar_bfree + 8 * j, qpar, wc, kErrFwd + 16, kPollSleepNs);
                     mbar_arrive_expect_tx(bar_bfull + 8 * j, C::kBChunk);
@@ -698,14 +712,42 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                 }
             }
         }
-    } else if (warp >= 12 && warp < 16) {
-        if (lane == 0) {
-            // ------------------------------------------------------------------ UMMA issuers
-            // Issuer i takes the ring positions i, i + 4, ...: chunks y, y + 2, ... (y = i / 2) of stream x = i % 2, the
-            // tiles 2t + x, accumulated into buffer 2 * (pair parity) + x.
-            const int i = warp - 12;
+    } else if (warp >= kIssuerWarp && warp < kIssuerWarp + kIssuers) {
+        if (lane == 0 && rank == 1) {
+            if (warp == kIssuerWarp) {
+                // -------------------------------------------------------------- forward slot-full to the even CTA
+                int rs[2] = {0, 0};
+                uint32_t ph[2] = {0, 0}, qpar = 0;
+                for (int ql = cta; ql < nq; ql += n_ctas, qpar ^= 1) {
+                    for (int tp = 0; tp < n_tp; ++tp) {
+                        for (int j = 0; j < kQChunks; ++j) {
+                            // this CTA's half of Q is part of what "full" promises
+                            if (tp == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrFwd + 15);
+#pragma unroll
+                            for (int sub = 0; sub < 2; ++sub) {
+                                const int s = (sub ? C::kStages0 : 0) + rs[sub];
+                                mbar_spin(bar_full + 8 * s, ph[sub], wc, kErrFwd + 17);
+                                // The copies have landed in this CTA's shared memory (the wait above saw them
+                                // complete); make them visible to the tensor core's proxy here, then signal without
+                                // a cluster-scope release (hundreds of cycles per call).
+                                fence_proxy_async_smem();
+                                mbar_arrive_cluster_relaxed(map_to_cta(bar_full + 8 * s, 0));
+                                if (++rs[sub] == (sub ? C::kStages1 : C::kStages0)) {
+                                    rs[sub] = 0;
+                                    ph[sub] ^= 1;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            // ------------------------------------------------------------------ UMMA issuers for the pair
+            // Issuer i takes the ring positions i, i + kIssuers, ...: chunks y, y + kIssuersPerStream, ... (y = i / 2) of
+            // stream x = i % 2, the tiles 2t + x, accumulated into buffer 2 * (pair parity) + x.
+            const int i = warp - kIssuerWarp;
             const int x = i & 1, y = i >> 1;
-            constexpr uint32_t idesc = make_idesc_bf16(128, HP, 0, 0);
+            constexpr uint32_t idesc = make_idesc_bf16(256, HP, 0, 0);
             const uint64_t desc_hi = make_smem_desc(0, 16, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
             const uint32_t desc_lo = static_cast<uint32_t>(make_smem_desc(0, 16, 1024, kSwizzle128));
             const uint32_t a_lo0 = desc_lo + ((s_base + C::kOffRing) >> 4);
@@ -715,9 +757,12 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
             const uint32_t my_tok = tok + 4 * x;
             int j = y, tp = 0, gtp = 0;
             uint32_t qpar = 0;
-            int s = i;
+            const int ring0 = x ? C::kStages0 : 0, ring_n = x ? C::kStages1 : C::kStages0;
+            static_assert(kIssuersPerStream < C::kStages1, "an issuer meets a slot again only after the stream's other issuers");
+            int rs = y;                     // chunk c of the stream sits in slot c mod ring_n of the stream's ring
             uint32_t ph = 0;
-            for (int c = y; c < total; c += 2) {
+            for (int c = y; c < total; c += kIssuersPerStream) {
+                const int s = ring0 + rs;
                 const int b = 2 * (gtp & 1) + x;
                 if (j == 0) mbar_spin(bar_tempty + 8 * b, ((gtp >> 1) & 1) ^ 1, wc, kErrFwd + 13);
                 if (tp == 0) mbar_wait(bar_bfull + 8 * j, qpar, wc, kErrFwd + 12);
@@ -728,18 +773,18 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                 const uint32_t d = tmem + b * HP;
                 const uint32_t a_lo = a_lo0 + s * (kChunkA >> 4);
                 const uint32_t b_lo = b_lo0 + j * (C::kBChunk >> 4);
-                umma_ss(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
+                umma_ss_2cta(d, desc_hi | a_lo, desc_hi | b_lo, idesc, j != 0);
 #pragma unroll
                 for (int kk = 1; kk < 4; ++kk)   // 32 bytes further along K = +2 in the address field
-                    umma_ss(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
+                    umma_ss_2cta(d, desc_hi | (a_lo + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, 1);
                 tc_fence_before_sync();
                 flag_store(my_tok, static_cast<uint32_t>(c + 1));
                 // The UMMAs on one accumulator complete in the order they were issued, so the commit behind a tile's
                 // last chunk covers the chunks the stream's other issuer put in before it.
-                umma_commit(bar_empty + 8 * s);
-                if (tp == n_tp - 1) umma_commit(bar_bfree + 8 * j);
-                if (j == kQChunks - 1) umma_commit(bar_tfull + 8 * b);
-                j += 2;
+                umma_commit_2cta_mask(bar_empty + 8 * s, 3);
+                if (tp == n_tp - 1) umma_commit_2cta_mask(bar_bfree + 8 * j, 3);
+                if (j == kQChunks - 1) umma_commit_2cta_mask(bar_tfull + 8 * b, 3);
+                j += kIssuersPerStream;
                 if (j >= kQChunks) {
                     j -= kQChunks;
                     ++gtp;
@@ -748,14 +793,14 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                         qpar ^= 1;
                     }
                 }
-                s += 4;
-                if (s >= kStages) {
-                    s -= kStages;
+                rs += kIssuersPerStream;
+                if (rs >= ring_n) {
+                    rs -= ring_n;
                     ph ^= 1;
                 }
             }
             if (*s_abort) {
-                umma_commit(bar_drain + 8 * i);
+                umma_commit_2cta_mask(bar_drain + 8 * i, 1);
                 mbar_wait_drain(bar_drain + 8 * i, 0, p.wait_limit);
             }
         }
@@ -764,6 +809,7 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
         const int quarter = warp & 3;
         const int g = warp >> 2;            // head half
         const int row = quarter * 32 + lane;
+        const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
         const uint64_t pol_stream = l2_policy_evict_first();
         const int t = threadIdx.x;
         // second pass: the row maximum found by the first pass, in base-2 units, fetched one query ahead
@@ -788,7 +834,7 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
             float keep_max[2] = {__int_as_float(0xff800000), __int_as_float(0xff800000)};
             unsigned long long keep_sum[2] = {0ull, 0ull};
             for (int tile = 0; tile < n_tiles; ++tile, ++gt) {
-                const int key = tile * kTileKeys + row;
+                const int key = tile * kTileKeys + static_cast<int>(rank) * 128 + row;
                 const int idx = key < p.topk ? __ldg(p.indices + static_cast<size_t>(qg) * p.topk + key) : -1;
                 const bool valid = slot_valid(idx, key, qm, p);
                 const int b = gt & 3;               // 2 * (pair parity) + tile of the pair
@@ -861,7 +907,8 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + 8 * b);     // the accumulator reads have completed
+                // the accumulator reads have completed (tcgen05.wait::ld), which is all the issuers need to know
+                if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * b);
             }
             // this warp's share of the query's row statistics: integer atomics, so the order in which the warps
             // arrive does not change the result
@@ -879,7 +926,8 @@ smla_fwd_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const KParams p
     abort_wind_down(s_abort);
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 12) tmem_dealloc(tmem, C::kTmemCols);
+    cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
+    if (warp == kIssuerWarp) tmem_dealloc_2cta(tmem, C::kTmemCols);
 }
 
 // Row statistics of the forward start at -inf (maximum) and 0 (sum).
