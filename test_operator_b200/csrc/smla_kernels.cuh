@@ -561,7 +561,7 @@ constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;
 template <int HP> struct Cfg {
     static constexpr int kBChunk = (HP / 2) * 128;                 // Q_j of this CTA's heads
-    static constexpr int kStages = 9;
+    static constexpr int kStages = HP == 128 ? 9 : 11;
     // every tile stream has ring slots of its own (a slot is then always filled by the same producer group, which has
     // seen its previous use: waits on a barrier's phase parity cannot be taken for the phase before last)
     static constexpr int kStages0 = (kStages + 1) / 2;             // stream 0: slots [0, kStages0)
