@@ -71,7 +71,7 @@ void schedule(int* chunks, int* dkv_pairs) {
 int auto_chunks(int h_pad) { return h_pad > 64 ? 0 : 2; }
 
 int auto_dkv_pairs(int h_pad, int resident) {
-    const double share = h_pad > 64 ? 0.50 : 0.58;
+    const double share = h_pad > 64 ? 0.50 : 0.60;
     int n = static_cast<int>(resident * share + 0.5);
     if (n < 1) n = 1;
     if (n > resident - 1) n = resident - 1;

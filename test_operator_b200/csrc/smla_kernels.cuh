@@ -177,7 +177,7 @@ constexpr int kTileKeys = 256;             // per pair; 128 per CTA
 constexpr int kChunkA = 128 * 128;         // 16 KB gathered chunk
 template <int HP> struct Cfg {
     static constexpr int NH = HP / 2;                  // heads whose Q / dO rows this CTA holds
-    static constexpr int kStages = 5;
+    static constexpr int kStages = HP == 128 ? 5 : 9;  // what the stacked Q / dO leaves of the shared memory
     static constexpr int kBHalf = NH * 128;            // one [NH heads x 64 col] chunk
     static constexpr int kBChunk = 2 * kBHalf;         // stacked [Q_j | dO_j]
     static constexpr int kOffB = 0;
@@ -1328,8 +1328,8 @@ namespace dq {
 constexpr int kThreads = 448;
 constexpr int kProducerWarps = 8;
 constexpr int kTileKeys = 64;
-constexpr int kStages = 2;
 template <int HP, int kSplit> struct Cfg {
+    static constexpr int kStages = (HP == 64 && kSplit <= 3) ? 3 : 2;   // what fits twice into an SM's shared memory
     static_assert(kSplit >= 1 && kSplit <= 4, "one UMMA covers the part: N = 64 kSplit <= 256");
     static constexpr int kKgBytes = kSplit * 8192;
     static constexpr int kDsBytes = (HP / 64) * 8192;
@@ -1351,6 +1351,7 @@ __global__ void __launch_bounds__(dq::kThreads, 2)
 smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
     using namespace dq;
     using C = Cfg<HP, kSplit>;
+    constexpr int kStages = C::kStages;
     constexpr int kParts = (kTotal + kSplit - 1) / kSplit;
     const int part = blockIdx.x % kParts;
     const int ql = blockIdx.x / kParts;
@@ -1412,8 +1413,9 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             }
         };
         load_idx(0);
+        int s = 0;
+        uint32_t ph = 1;                    // parity that means "stage free" for the current pass over the ring
         for (int tile = 0; tile < n_tiles; ++tile) {
-            const int s = tile % kStages;
             const char* src[2];
             uint32_t nb[2];   // 0: slot out of range, read nothing and land zeros (no shared stand-in row: it would be a hot spot)
 #pragma unroll
@@ -1423,25 +1425,34 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
                 src[i] = kvb + static_cast<size_t>(row >= 0 ? row : 0) * (kDQK * 2);
             }
             load_idx(tile + 1);
-            mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 1, kPollSleepNs);
+            mbar_wait(bar_empty + 8 * s, ph, wc, kErrDq + 1, kPollSleepNs);
             const uint32_t d = dst0 + s * C::kStage;
             for (int c = 0; c < n_ch; ++c) {
                 cp_async16_zfill_hint(d + c * 8192, src[0] + c * 128, nb[0], pol_keep);
                 cp_async16_zfill_hint(d + c * 8192 + 32 * 128, src[1] + c * 128, nb[1], pol_keep);
             }
             cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+            if (++s == kStages) {
+                s = 0;
+                ph ^= 1;
+            }
         }
     } else if (warp == 13) {
         if (lane == 0) tma_prefetch_desc(&tm_ds);
         const uint64_t pol_stream = l2_policy_evict_first();
         if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 1;
             for (int tile = 0; tile < n_tiles; ++tile) {
-                const int s = tile % kStages;
-                mbar_wait(bar_empty + 8 * s, ((tile / kStages) & 1) ^ 1, wc, kErrDq + 4, kPollSleepNs);
+                mbar_wait(bar_empty + 8 * s, ph, wc, kErrDq + 4, kPollSleepNs);
                 const uint32_t dst = s_base + s * C::kStage;
                 mbar_arrive_expect_tx(bar_full + 8 * s, C::kDsBytes);
                 // box = 64 keys of every head block -> [HP/8][64 keys][8 heads]
                 tma_load_4d_hint(dst + C::kKgBytes, &tm_ds, 0, tile * (kTileKeys / 32), 0, p.scr0 + ql, bar_full + 8 * s, pol_stream);
+                if (++s == kStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
     } else if (warp == 12) {
@@ -1454,9 +1465,10 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
             const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc(0, 128, 1024, kSwizzleNone)) + ((s_base + C::kKgBytes) >> 4);
             const uint64_t b_hi = make_smem_desc(0, 8192, 1024, kSwizzle128) & 0xFFFFFFFF00000000ull;
             const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(0, 8192, 1024, kSwizzle128)) + (s_base >> 4);
+            int s = 0;
+            uint32_t ph = 0;
             for (int tile = 0; tile < n_tiles; ++tile) {
-                const int s = tile % kStages;
-                mbar_spin(bar_full + 8 * s, (tile / kStages) & 1, wc, kErrDq + 2);
+                mbar_spin(bar_full + 8 * s, ph, wc, kErrDq + 2);
                 fence_proxy_async_smem();
                 tc_fence_after_sync();
                 const uint32_t a_lo = a_lo0 + s * (C::kStage >> 4), b_lo = b_lo0 + s * (C::kStage >> 4);
@@ -1466,6 +1478,10 @@ smla_dq_kernel(const __grid_constant__ CUtensorMap tm_ds, const KParams p) {
                     umma_ss(tmem, a, b_hi | (b_lo + ks * (2048 >> 4)), idesc1, (tile | ks) != 0);
                 }
                 umma_commit(bar_empty + 8 * s);
+                if (++s == kStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
             umma_commit(bar_acc);
             if (*s_abort) {   // winding down: nothing of this thread's may still be in the tensor pipe at dealloc
