@@ -119,11 +119,6 @@ __device__ __noinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity, long
     }
 }
 
-// Plain arrival on a barrier of this CTA.
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
 // ---- plain shared-memory counter as a hand-over between two threads of a CTA ------------------------------
 // An mbarrier arrival takes ~180 cycles to become visible to a poller; a volatile word takes a few tens.
 __device__ __forceinline__ void flag_store(uint32_t saddr, uint32_t v) {
